@@ -4,7 +4,8 @@ from .base import LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry
 from .registry import (architecture_name, load_config, register_architecture, resolve_config,
                        supported_architectures)
 from .qwen3 import Qwen3Config
+from .zupilorn import ZupilornConfig
 
-__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config",
+__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "ZupilornConfig",
            "architecture_name", "load_config", "register_architecture", "resolve_config",
            "supported_architectures"]

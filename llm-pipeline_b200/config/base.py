@@ -33,10 +33,11 @@ class LayerSpec:
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]          # None: the layer has a mixer only
     mixer_norm: Optional[PartSpec] = None
     feed_forward_norm: Optional[PartSpec] = None
     norms: Dict[str, PartSpec] = field(default_factory=dict)
+    depth_mix: Optional[PartSpec] = None      # how the layer's result is combined with those of the layers before it
 
     def named_norms(self) -> Dict[str, PartSpec]:
         out: Dict[str, PartSpec] = {}

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (``config.json["architectures"][0]``) to its typed
+"""One registry from an architecture's name (``config.json["architectures"][0]``, or its ``"architecture"``) to its typed
 configuration. The reference keeps a dictionary from a name to an entry with required keys and a
 ``register`` call that checks them (src/llm_pipeline/core/registry.py:50-62,102-109); its engine
 hard-wires the Qwen3 factory (src/llm_pipeline/inference/qwen3_engine.py:175). Here the entry
@@ -29,6 +29,8 @@ def architecture_name(config_json: Dict[str, Any]) -> str:
     names = config_json.get("architectures") or []
     if names:
         return str(names[0])
+    if isinstance(config_json.get("architecture"), str):
+        return config_json["architecture"]
     model_type = config_json.get("model_type")
     for name, cls in _ARCHITECTURES.items():
         if model_type is not None and getattr(cls, "model_type", None) == model_type:

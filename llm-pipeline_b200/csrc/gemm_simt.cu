@@ -11,7 +11,12 @@
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_nt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, const void* __restrict__ bias, int bias_bf16,
-               TO* __restrict__ C, int M, int N, int K, long lda, long ldw, long ldc) {
+               TO* __restrict__ C, int M, int N, int K, long lda, long ldw, long ldc, long batch_a = 0, long batch_w = 0,
+               long batch_c = 0) {
+    // blockIdx.z counts the products of a batch: each has its own A, W and C, the given strides apart
+    A += (size_t)blockIdx.z * batch_a;
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     __shared__ float As[GT_BK][GT_BM + 4];
     __shared__ float Ws[GT_BK][GT_BN + 4];
     const int tid = threadIdx.x;
@@ -85,4 +90,30 @@ LLMP_API int llmp_gemm_simt(const void* A, const void* W, const void* bias, int 
         return 1;
     }
     return llmp_check_launch("gemm_simt");
+}
+
+// A batch of such products in one launch: product b reads A + b * batch_a and W + b * batch_w and writes C + b * batch_c
+// (strides in elements; rows of any of them may lie further apart than they are long, so one product per head
+// can read and write the heads of a [tokens, heads, size] tensor in place).
+LLMP_API int llmp_gemm_simt_batched(const void* A, const void* W, void* C, int in_dtype, int out_dtype, int batch, int M, int N,
+                                    int K, long lda, long ldw, long ldc, long batch_a, long batch_w, long batch_c,
+                                    cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    LLMP_REQUIRE(K > 0, "batched gemm: bad K %d", K);
+    LLMP_REQUIRE((M + GT_BM - 1) / GT_BM <= 65535 && batch <= 65535, "batched gemm: too many rows %d or products %d", M, batch);
+    dim3 grid((N + GT_BN - 1) / GT_BN, (M + GT_BM - 1) / GT_BM, batch);
+    if (in_dtype == LLMP_F32 && out_dtype == LLMP_F32)
+        gemm_nt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)A, (const float*)W, nullptr, 0, (float*)C, M, N, K,
+                                                               lda, ldw, ldc, batch_a, batch_w, batch_c);
+    else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_BF16)
+        gemm_nt_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, nullptr, 0, (bf16*)C, M, N, K, lda,
+                                                             ldw, ldc, batch_a, batch_w, batch_c);
+    else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_F32)
+        gemm_nt_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, nullptr, 0, (float*)C, M, N, K,
+                                                              lda, ldw, ldc, batch_a, batch_w, batch_c);
+    else {
+        llmp_set_error("batched gemm: unsupported type combination in=%d out=%d", in_dtype, out_dtype);
+        return 1;
+    }
+    return llmp_check_launch("gemm_simt_batched");
 }

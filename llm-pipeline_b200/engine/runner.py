@@ -72,6 +72,7 @@ class _DecodeGraph:
         self.req_ids = None          # the requests of the last step in row order, each with its admission number
         self.table_lens = None       # per cache group and row: pages of the block table already in the buffer
         self.pieces = None           # a model that is captured in pieces: [_Piece] in the order of the schedule
+        self.history = None          # the residual stream's history of layer results (models with a depth mix), shared by the pieces
 
 
 class _Piece:
@@ -448,7 +449,9 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             piece.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(piece.graph, pool=pool):
-                stream = model.begin(ctx) if k == 0 else ResidualStream(piece.inlet)
+                stream = model.begin(ctx) if k == 0 else ResidualStream(piece.inlet, slot.history)
+                if k == 0:
+                    slot.history = stream.history        # layer results that a model with a depth mix keeps: one buffer for all pieces
                 model.run_layers(ctx, self._views, stream, first, end)
                 if k + 1 < len(runs):
                     piece.outlet = stream.settle()
@@ -469,7 +472,7 @@ class ModelRunner:
             # eager layers: the step's arrays are the captured step's; what the layers note for themselves is not kept
             eager = copy.copy(ctx)
             eager.memo = {}
-            stream = ResidualStream(residual)
+            stream = ResidualStream(residual, slot.history)
             model.run_layers(eager, self._views, stream, piece.first, piece.end)
             residual = stream.settle()
         slot.logits = slot.pieces[-1].outlet

@@ -33,11 +33,17 @@ class Model:
         self.blocks = []
         for layer in spec.layers:
             block_cls = lookup("block", layer.block)
-            self.blocks.append(block_cls(_make("mixer", layer.mixer), _make("feed_forward", layer.feed_forward),
-                                         norms={name: _make("norm", norm) for name, norm in layer.named_norms().items()}))
+            extras = {"depth_mix": _make("depth_mix", layer.depth_mix)} if layer.depth_mix is not None else {}
+            self.blocks.append(block_cls(_make("mixer", layer.mixer),
+                                         _make("feed_forward", layer.feed_forward) if layer.feed_forward is not None else None,
+                                         norms={name: _make("norm", norm) for name, norm in layer.named_norms().items()},
+                                         **extras))
         self.final_norm = _make("norm", spec.final_norm)
         self.head = _make("head", spec.head)
         self.schedule = list(spec.schedule)
+        # results the residual stream keeps for layers that mix over depth: the embedding's output and one per layer
+        mixes = [block.depth_mix.index for block in self.blocks if block.depth_mix is not None]
+        self.history_slots = max(mixes) + 1 if mixes else 0
         # Which execution owns (writes) each cache id: the first that names it.
         self._owner: Dict[int, int] = {}
         for i, entry in enumerate(self.schedule):
@@ -101,7 +107,7 @@ class Model:
         self.device, self.dtype = torch.device(device), dtype
         # A tensor two parts read (the table of a tied head) is moved to the device once.
         tied_to = self.spec.head.args.get("tied_to")
-        tied = {f"{tied_to}.weight"} if tied_to else set()
+        tied = {self.spec.head.args.get("tied_name") or f"{tied_to}.weight"} if tied_to else set()
         shared: Dict[tuple, torch.Tensor] = {}
 
         def get(name: str, role: str) -> torch.Tensor:
@@ -133,7 +139,12 @@ class Model:
         begin_step()
         with nvtx_range("positions and embedding"):
             ctx.position_tables = {name: part.tables(ctx) for name, part in self.positions.items()}
-            return ResidualStream(self.embedding.forward(ctx))
+            residual = self.embedding.forward(ctx)
+            history = None
+            if self.history_slots:
+                history = torch.empty((self.history_slots,) + tuple(residual.shape), dtype=torch.float32, device=residual.device)
+                history[0].copy_(residual)
+            return ResidualStream(residual, history)
 
     def run_layers(self, ctx, caches, stream: ResidualStream, first: int, end: int) -> None:
         """The scheduled executions first .. end - 1 on ``stream``."""

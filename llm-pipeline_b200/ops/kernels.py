@@ -57,6 +57,16 @@ _SIGNATURES = {
     "llmp_entropy": [_P, _L, _I, _I, _F, _P, _P],
     "llmp_bounded_wait_check": [_P, _I, _P, _P],
     "llmp_gemm_stream_chain": [_P, _I, _I, _P, _P, _P],
+    "llmp_gemm_simt_batched": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _P],
+    "llmp_embedding_norm": [_P, _P, _I, _P, _I, _F, _F, _P, _I, _I, _I, _P],
+    "llmp_add_norm_mix": [_P, _P, _I, _P, _I, _F, _F, _P, _L, _P, _I, _P, _I, _F, _F, _P, _I, _P, _I, _I, _P],
+    "llmp_poly_norm": [_P, _I, _L, _P, _F, _P, _I, _I, _I, _P],
+    "llmp_softcap": [_P, _L, _F, _P],
+    "llmp_min_gru": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P],
+    "llmp_latent_kv_post": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _F, _P, _P, _I, _P, _P, _I, _P],
+    "llmp_latent_attention": [_P, _L, _L, _P, _L, _L, _P, _I, _P, _I, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P],
+    "llmp_route_topk": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _P],
+    "llmp_expert_rows": [_P, _P, _P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P],
 }
 _bound = {}
 launch_count = 0   # kernels of this library launched so far (captured launches count once per capture)
@@ -714,3 +724,191 @@ def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor, out_u:
     _call("llmp_sample", _ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(params), _ptr(out),
           _ptr(out_u), _stream())
     return out
+
+
+# ---- parts beyond the dense pre-norm decoder: norms around a sublayer, depth mixing, recurrent and latent mixers, experts ----
+def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b, m, :] = a[b, m, :] @ w[b]^T for a [B, M, K], w [B, N, K], out [B, M, N] on the CUDA cores with float32 sums.
+    Any of the three may be a view whose batches and rows lie apart (the heads of a [tokens, heads, size] tensor
+    transposed to [heads, tokens, size]); only the last axis must be dense."""
+    B, M, K = a.shape
+    N = w.shape[1]
+    _need(w.shape == (B, N, K) and out.shape == (B, M, N), "batched gemm shapes do not match")
+    _need(a.dtype == w.dtype and a.stride(2) == 1 and w.stride(2) == 1 and out.stride(2) == 1,
+          "batched gemm operands must have one type and a dense last axis")
+    _call("llmp_gemm_simt_batched", _ptr(a), _ptr(w), _ptr(out), dtype_code(a.dtype), dtype_code(out.dtype), B, M, N, K,
+          a.stride(1), w.stride(1), out.stride(1), a.stride(0), w.stride(0), out.stride(0), _stream())
+    return out
+
+
+def embedding_norm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, offset: float, eps: float,
+                   out: torch.Tensor) -> torch.Tensor:
+    """out[n] = rms_norm(table[ids[n]]) * (offset + weight), float32."""
+    _i32(ids, "ids")
+    _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be a contiguous matrix")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (ids.numel(), table.shape[1]),
+          "embedding output must be float32 [tokens, hidden]")
+    _need(weight.numel() == table.shape[1] and weight.is_contiguous(), "norm weight has the wrong size")
+    _call("llmp_embedding_norm", _ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(weight), dtype_code(weight.dtype),
+          float(offset), float(eps), _ptr(out), ids.numel(), table.shape[1], table.shape[0], _stream())
+    return out
+
+
+def add_norm_mix(residual: torch.Tensor, *, delta: Optional[torch.Tensor] = None, delta_weight: Optional[torch.Tensor] = None,
+                 delta_offset: float = 0.0, delta_eps: float = 0.0, history: Optional[torch.Tensor] = None,
+                 mix: Optional[torch.Tensor] = None, index: int = 0, weight: Optional[torch.Tensor] = None, offset: float = 0.0,
+                 eps: float = 0.0, out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The residual stream's norm kernel in its general form, per row r (``rows`` selects rows and leaves the stream as it is):
+    y = delta[r], normed by (delta_offset + delta_weight) if that is given; x = residual[r] + y; with ``history``
+    [slots, tokens, width]: history[index][r] = x and x = sum_{j <= index} mix[j] history[j][r]; residual[r] = x;
+    out = rms_norm(x) * (offset + weight) if ``out`` is given."""
+    T, H = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "residual must be a contiguous float32 matrix")
+    M = rows.numel() if rows is not None else T
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.shape == residual.shape, "delta must match the residual's shape")
+    if delta_weight is not None:
+        _need(delta_weight.numel() == H and delta_weight.is_contiguous(), "the addend's norm weight has the wrong size")
+    if history is not None:
+        _need(history.dtype == torch.float32 and history.is_contiguous() and history.dim() == 3 and
+              tuple(history.shape[1:]) == (T, H) and 0 <= index < history.shape[0], "history must be float32 [slots, tokens, width]")
+        _need(mix is not None and mix.dtype == torch.float32 and mix.is_contiguous() and mix.numel() >= index + 1,
+              "mixing weights must be float32, one per result so far")
+    if out is not None:
+        _need(out.is_contiguous() and out.shape == (M, H) and weight is not None and weight.numel() == H and weight.is_contiguous(),
+              "norm output or weight has the wrong shape")
+    if rows is not None:
+        _i32(rows, "rows")
+    _call("llmp_add_norm_mix", _ptr(residual), _ptr(delta), dtype_code(delta.dtype) if delta is not None else F32,
+          _ptr(delta_weight), dtype_code(delta_weight.dtype) if delta_weight is not None else F32, float(delta_offset),
+          float(delta_eps), _ptr(history), T * H, _ptr(mix), int(index), _ptr(weight),
+          dtype_code(weight.dtype) if weight is not None else F32, float(offset), float(eps), _ptr(out),
+          dtype_code(out.dtype) if out is not None else F32, _ptr(rows), M, H, _stream())
+    return out
+
+
+def poly_norm(z: torch.Tensor, act: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps); ``act`` = float32 (a, b, c, e)."""
+    N, F = z.shape
+    _need(z.stride(1) == 1 and out.is_contiguous() and out.shape == (N, F), "poly_norm shapes do not match")
+    _need(act.dtype == torch.float32 and act.numel() == 4 and act.is_contiguous(), "poly_norm takes four float32 coefficients")
+    _call("llmp_poly_norm", _ptr(z), dtype_code(z.dtype), z.stride(0), _ptr(act), float(eps), _ptr(out), dtype_code(out.dtype),
+          N, F, _stream())
+    return out
+
+
+def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place: logits = cap * tanh(logits / cap)."""
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "softcap takes contiguous float32 logits")
+    _call("llmp_softcap", _ptr(logits), logits.numel(), float(cap), _stream())
+    return logits
+
+
+_gru_chunk: Optional[int] = None
+
+
+def min_gru_chunk() -> int:
+    """Tokens per chunk of the parallel form of ``min_gru``; portions longer than this need scratch."""
+    global _gru_chunk
+    if _gru_chunk is None:
+        fn = library().llmp_min_gru_chunk
+        fn.argtypes = []
+        fn.restype = _I
+        _gru_chunk = int(fn())
+    return _gru_chunk
+
+
+def min_gru(p: torch.Tensor, bias: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor,
+            state: torch.Tensor, out: torch.Tensor, max_q_len: int) -> torch.Tensor:
+    """The minGRU recurrence over the step's tokens. ``p`` float32 [tokens, 3 W] (gate, candidate and output-gate
+    products), ``bias`` float32 [2 W], ``state`` float32 [slots, 2, W] (see csrc/min_gru.cu), ``out`` [tokens, W]."""
+    N, three_w = p.shape
+    W = three_w // 3
+    R = slots.numel()
+    _need(p.dtype == torch.float32 and p.is_contiguous() and three_w == 3 * W, "min_gru takes float32 products [tokens, 3 W]")
+    _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == 2 * W, "min_gru takes float32 biases [2 W]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (2, W), "min_gru state must be float32 [slots, 2, W]")
+    _need(out.is_contiguous() and out.shape == (N, W), "min_gru output has the wrong shape")
+    for t, name in ((q_start, "q_start"), (slots, "slots"), (positions, "positions")):
+        _i32(t, name)
+    scratch = None
+    chunk = min_gru_chunk()
+    if max_q_len > chunk:
+        scratch = torch.empty((2, R, -(-max_q_len // chunk), W), dtype=torch.float32, device=p.device)
+    _call("llmp_min_gru", _ptr(p), _ptr(bias), _ptr(q_start), _ptr(slots), _ptr(positions), _ptr(state), _ptr(out),
+          dtype_code(out.dtype), _ptr(scratch), R, W, int(max_q_len), _stream())
+    return out
+
+
+def latent_kv_post(qd: torch.Tensor, num_heads: int, dim: int, rot: int, rank: int, norm_weight: torch.Tensor, eps: float,
+                   cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dims: int, slots: Optional[torch.Tensor],
+                   pages: Optional[torch.Tensor]) -> None:
+    """In place on ``qd`` [tokens, heads (dim + rot) + rank + rot]: every head's last ``rot`` query entries are rotated;
+    the row's last rank + rot entries become a cache row (the first ``rank`` RMS-normed with ``norm_weight``, the rest
+    rotated) written to the token's slot of ``pages`` [pages, page_size, rank + rot]."""
+    N = qd.shape[0]
+    _need(qd.stride(1) == 1 and qd.shape[1] == num_heads * (dim + rot) + rank + rot, "latent_kv_post: the product has the wrong width")
+    _need(norm_weight.numel() == rank and norm_weight.is_contiguous(), "latent norm weight has the wrong size")
+    if rot_dims:
+        _need(cos is not None and sin is not None and cos.shape == (N, rot_dims // 2) and cos.dtype == torch.float32 and
+              cos.is_contiguous() and sin.is_contiguous(), "rotary tables must be float32 [tokens, rotated / 2]")
+    if pages is not None:
+        _need(pages.dtype == qd.dtype and pages.is_contiguous() and pages.shape[2] == rank + rot and slots is not None,
+              "latent pages have the wrong layout")
+        _i32(slots, "slots")
+    _call("llmp_latent_kv_post", _ptr(qd), dtype_code(qd.dtype), qd.stride(0), num_heads, dim, rot, rank, _ptr(norm_weight),
+          dtype_code(norm_weight.dtype), float(eps), _ptr(cos), _ptr(sin), int(rot_dims), _ptr(slots) if pages is not None else None,
+          _ptr(pages), N, _stream())
+
+
+def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor,
+                     token_request: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, scale: float) -> torch.Tensor:
+    """Causal attention of rows (token, head) over latent cache rows. ``q_lat`` [tokens, heads, rank] and ``q_rot``
+    [tokens, heads, rot] (views with a dense last axis), ``pages`` [pages, page_size, rank + rot], ``out`` [tokens,
+    heads, rank]: the softmax-weighted sum of the visible rows' first ``rank`` entries."""
+    N, H, rank = q_lat.shape
+    rot = q_rot.shape[2]
+    _need(q_rot.shape[:2] == (N, H) and out.shape == (N, H, rank), "latent attention shapes do not match")
+    _need(q_lat.stride(2) == 1 and (rot == 0 or q_rot.stride(2) == 1) and out.stride(2) == 1, "latent attention needs dense last axes")
+    _need(q_lat.dtype == pages.dtype == out.dtype == q_rot.dtype, "latent attention operands must have one type")
+    _need(pages.is_contiguous() and pages.dim() == 3 and pages.shape[2] == rank + rot, "latent pages have the wrong layout")
+    _i32(tables, "tables"); _i32(token_request, "token_request"); _i32(positions, "positions")
+    _call("llmp_latent_attention", _ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1),
+          _ptr(pages), dtype_code(pages.dtype), _ptr(tables), tables.shape[1], _ptr(token_request), _ptr(positions), _ptr(out),
+          out.stride(0), out.stride(1), N, H, rank, rot, pages.shape[1], float(scale), _stream())
+    return out
+
+
+def route_topk(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """ids[n, :], weights[n, :] = the ``top`` experts with the largest sigmoid(w_router h[n]) and those scores; float32 logits."""
+    N, Hd = h.shape
+    E = w_router.shape[0]
+    _need(h.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == Hd,
+          "the router matrix must be float32 [experts, width]")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (N, top) and weights.dtype == torch.float32 and
+          weights.is_contiguous() and weights.shape == (N, top), "route_topk outputs must be int32 and float32 [tokens, top]")
+    _call("llmp_route_topk", _ptr(h), dtype_code(h.dtype), _ptr(w_router), int(top), _ptr(ids), _ptr(weights), N, Hd, E, _stream())
+
+
+def expert_rows(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                limit: float, out: torch.Tensor) -> torch.Tensor:
+    """out[n] = sum_k Wd[e] act(weights[n, k] * (Wg[e] h[n]), weights[n, k] * (Wu[e] h[n])) with e = ids[n, k], float32.
+    ``w_gate_up`` [experts, 2 ff, width] (gate rows, then up rows), ``w_down`` [experts, width, ff]. Reads an expert once
+    per token that chose it: for the few rows of a decode step."""
+    N, Hd = h.shape
+    E, two_f, _ = w_gate_up.shape
+    F = two_f // 2
+    top = ids.shape[1]
+    _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.shape == (E, 2 * F, Hd) and
+          w_down.shape == (E, Hd, F) and h.dtype == w_gate_up.dtype == w_down.dtype, "expert matrices have the wrong layout")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (N, Hd), "expert output must be float32 [tokens, width]")
+    y = torch.empty((N * top, F), dtype=h.dtype, device=h.device)
+    _call("llmp_expert_rows", _ptr(h), _ptr(w_gate_up), _ptr(w_down), dtype_code(h.dtype), _ptr(ids), _ptr(weights), float(limit),
+          _ptr(y), _ptr(out), N, top, Hd, F, _stream())
+    return out
+
+
+def routed_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                   limit: float, out: torch.Tensor) -> torch.Tensor:
+    """The experts' work for a step's rows, by the kernel that suits their number (``expert_rows`` for few)."""
+    return expert_rows(h, w_gate_up, w_down, ids, weights, limit, out)

@@ -414,3 +414,21 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     else:
         out = torch.mm(x, weight.t(), out_dtype=out_dtype)
     return out if bias is None else out.add_(bias.to(out.dtype))
+
+
+def batched_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = x[b] @ weight[b]^T for x [B, M, K], weight [B, N, K], out [B, M, N]: one product per head. ``x`` and
+    ``out`` may be transposed views of [M, B, .] tensors (the heads of a step's rows), so nothing is copied. float32
+    operands: the CUDA-core kernel (a true 32-bit product). bfloat16 operands: the library's batched product for many
+    rows, the CUDA-core kernel (float32 sums) for the few rows of a decode step, where the product is a few
+    microseconds either way and the own kernel costs the host a plain call."""
+    B, M, K = x.shape
+    if M == 0 or B == 0:
+        return out
+    if x.dtype == torch.bfloat16 and M >= BATCHED_LIBRARY_MIN_ROWS:
+        torch.bmm(x, weight.transpose(1, 2), out=out)
+        return out
+    return kernels.gemm_batched(x, weight, out)
+
+
+BATCHED_LIBRARY_MIN_ROWS = int(os.environ.get("LLMP_B200_BATCHED_LIBRARY_MIN_M", "64"))

@@ -1,11 +1,12 @@
 """Parts: norm, position encoding, mixer, feed-forward, embedding, head, block arrangement."""
 
-from .base import (Block, Embedding, FeedForward, Head, LayerCache, Mixer, Norm, Part, PositionEncoding,
+from .base import (Block, DepthMix, Embedding, FeedForward, Head, LayerCache, Mixer, Norm, Part, PositionEncoding,
                    ResidualStream)
-from .registry import (kinds, lookup, register_block, register_embedding, register_feed_forward, register_head,
+from .registry import (kinds, lookup, register_block, register_depth_mix, register_embedding, register_feed_forward, register_head,
                        register_mixer, register_norm, register_position)
-from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401  (register the built-in kinds)
+from . import (attention, block, depth_mix, embedding, experts, feed_forward, latent_attention, norm, position,  # noqa: F401
+               recurrent)  # noqa: F401  (register the built-in kinds)
 
-__all__ = ["Block", "Embedding", "FeedForward", "Head", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding",
-           "ResidualStream", "kinds", "lookup", "register_block", "register_embedding", "register_feed_forward",
+__all__ = ["Block", "DepthMix", "Embedding", "FeedForward", "Head", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding",
+           "ResidualStream", "kinds", "lookup", "register_block", "register_depth_mix", "register_embedding", "register_feed_forward",
            "register_head", "register_mixer", "register_norm", "register_position"]

@@ -13,6 +13,7 @@ works on the tensors of one step. No part knows which model it is in.
   ``state_spec()`` tell the cache manager what it needs.
 * ``FeedForward.forward(x, ctx) -> (out, bias)``: works on each token alone.
 * ``Block.forward(stream, ctx, cache)``: the arrangement of the above around the residual stream.
+* ``DepthMix``: optional per layer; weights with which the results of all layers so far are summed into what goes on.
 
 Optional, for the few rows of a decode step (``ops/linear.py``: a norm between two streaming products folded into
 them): a mixer or feed-forward with ``forward_deferred(...)`` may return its last product as a ``PendingProduct``; a
@@ -49,19 +50,42 @@ class LayerCache:
 
 class ResidualStream:
     """The hidden state between parts: a float32 residual ``[tokens, hidden]`` and a pending
-    addend in the compute type (with an optional bias vector) that the next norm folds in."""
+    addend (with an optional bias vector) that the next norm folds in.
 
-    def __init__(self, residual: torch.Tensor):
+    Two more things may be pending, for blocks that ask for them: a norm of the addend itself (``add(..., norm=)``: the
+    addend is normed before it is added), and a mix over depth (``mix(weights, index)``: once the addend is in, the
+    residual is this layer's result; it is kept as ``history[index]`` and replaced by ``sum_j weights[j] history[j]``,
+    j = 0 .. index). ``history`` is float32 ``[results, tokens, hidden]`` with the embedding's output at 0; only models
+    with such a mix have one. The next norm kernel does all of it in one pass over the row."""
+
+    def __init__(self, residual: torch.Tensor, history: Optional[torch.Tensor] = None):
         self.residual = residual
         self._pending = None
         self.pending_bias: Optional[torch.Tensor] = None
+        self.pending_norm = None                      # a Norm part with ``weight`` and ``eps``: norms the addend
+        self.pending_mix: Optional[Tuple[torch.Tensor, int]] = None
+        self.history = history
 
-    def add(self, delta, bias: Optional[torch.Tensor] = None) -> None:
+    def add(self, delta, bias: Optional[torch.Tensor] = None, norm=None) -> None:
         """``delta``: a tensor, or a product not yet taken (``ops.linear.PendingProduct``) that the next norm may
-        fold into its own work."""
-        if self._pending is not None:
+        fold into its own work. ``norm``: the addend passes through this norm first."""
+        if self._pending is not None or self.pending_mix is not None:
             raise RuntimeError("the residual stream already holds a pending addend")
-        self._pending, self.pending_bias = delta, bias
+        self._pending, self.pending_bias, self.pending_norm = delta, bias, norm
+
+    def mix(self, weights: torch.Tensor, index: int) -> None:
+        """What the stream holds once the pending addend is in is result ``index``; what goes on is the weighted sum of
+        the results 0 .. index (``weights``: float32, one per result)."""
+        if self.history is None:
+            raise RuntimeError("this stream keeps no history of layer results; the model's specification names no depth mix")
+        if self.pending_mix is not None:
+            raise RuntimeError("the residual stream already holds a pending mix")
+        self.pending_mix = (weights, int(index))
+
+    @property
+    def plain(self) -> bool:
+        """Nothing is pending but, at most, an addend with its bias."""
+        return self.pending_norm is None and self.pending_mix is None
 
     @property
     def pending(self) -> Optional[torch.Tensor]:
@@ -74,9 +98,32 @@ class ResidualStream:
     def pending(self, delta) -> None:
         self._pending = delta
 
+    def fold(self, weight: Optional[torch.Tensor] = None, eps: float = 0.0, out: Optional[torch.Tensor] = None,
+             rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Everything pending in one kernel, and the RMS norm of the result by ``weight`` into ``out`` if given. With
+        ``rows`` only those rows are computed and the stream stays as it is."""
+        from ..ops import kernels
+
+        delta = self.pending
+        if delta is not None and self.pending_bias is not None:
+            delta = delta.float() + self.pending_bias.float()
+        norm, mixing = self.pending_norm, self.pending_mix
+        kernels.add_norm_mix(self.residual, delta=delta,
+                             delta_weight=norm.weight if norm is not None and delta is not None else None,
+                             delta_eps=norm.eps if norm is not None else 0.0,
+                             history=self.history if mixing is not None else None,
+                             mix=mixing[0] if mixing is not None else None, index=mixing[1] if mixing is not None else 0,
+                             weight=weight, eps=eps, out=out, rows=rows)
+        if rows is None:
+            self._pending, self.pending_bias, self.pending_norm, self.pending_mix = None, None, None, None
+        return out
+
     def settle(self) -> torch.Tensor:
         """Add what is pending into the residual and return it: the whole state of the stream in one float32 tensor
         (between pieces of a step that are captured apart; the norms fold the addend in on their own otherwise)."""
+        if not self.plain:
+            self.fold()
+            return self.residual
         pending = self.pending
         if pending is not None:
             self.residual = self.residual + pending.float()
@@ -88,7 +135,7 @@ class ResidualStream:
     def take_pending_product(self) -> Optional[PendingProduct]:
         """The pending addend if it is a product not yet taken and without bias, which is then the caller's to add;
         else None, and nothing changes."""
-        if isinstance(self._pending, PendingProduct) and self.pending_bias is None:
+        if isinstance(self._pending, PendingProduct) and self.pending_bias is None and self.plain:
             product, self._pending = self._pending, None
             return product
         return None
@@ -160,6 +207,16 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class DepthMix(Part):
+    """How a layer's result is combined with the results of the layers before it (and the embedding's output) into
+    what the next layer reads. ``weights`` (float32, on the device after ``load``) holds one weight per result so far;
+    ``index`` is the place of this layer's result among them. A block that has one calls
+    ``stream.mix(self.depth_mix.weights, self.depth_mix.index)`` at its end."""
+
+    weights: Optional[torch.Tensor] = None
+    index: int = 0
+
+
 class Embedding(Part):
     def forward(self, ctx) -> torch.Tensor:
         """float32 residual [tokens, hidden] of ctx.token_ids"""
@@ -179,18 +236,24 @@ class Block:
 
     NORMS: Tuple[str, ...] = ()
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Optional[Norm] = None,
-                 feed_forward_norm: Optional[Norm] = None, norms: Optional[Dict[str, Norm]] = None):
-        self.mixer, self.feed_forward = mixer, feed_forward
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Optional[Norm] = None,
+                 feed_forward_norm: Optional[Norm] = None, norms: Optional[Dict[str, Norm]] = None,
+                 depth_mix: Optional["DepthMix"] = None):
+        self.mixer, self.feed_forward, self.depth_mix = mixer, feed_forward, depth_mix
         self.norms: Dict[str, Norm] = {}
         if mixer_norm is not None:
             self.norms["mixer"] = mixer_norm
         if feed_forward_norm is not None:
             self.norms["feed_forward"] = feed_forward_norm
         self.norms.update(norms or {})
-        missing = [name for name in self.NORMS if name not in self.norms]
+        missing = [name for name in self.needed_norms() if name not in self.norms]
         if missing:
             raise ValueError(f"a {type(self).__name__} needs the norms {list(self.NORMS)}; the layer lacks {missing}")
+
+    def needed_norms(self) -> Tuple[str, ...]:
+        """The norms this layer cannot be built without (``NORMS``, unless the kind says otherwise for a layer
+        without a feed-forward)."""
+        return self.NORMS
 
     @property
     def mixer_norm(self) -> Optional[Norm]:
@@ -201,7 +264,8 @@ class Block:
         return self.norms.get("feed_forward")
 
     def parts(self):
-        return tuple(self.norms.values()) + (self.mixer, self.feed_forward)
+        return tuple(self.norms.values()) + tuple(
+            part for part in (self.mixer, self.feed_forward, self.depth_mix) if part is not None)
 
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
         raise NotImplementedError

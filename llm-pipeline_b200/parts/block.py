@@ -31,3 +31,28 @@ class PreNormResidualBlock(Block):
         if deferred is not None and getattr(consumer, "takes_scaled_rows", False):
             return deferred(stream, ctx)
         return norm.add_norm(stream, ctx)
+
+
+@register_block("sandwich_norm_residual")
+class SandwichNormResidualBlock(Block):
+    """A norm before and after each sublayer: ``x += norm_out(mixer(norm_in(x)))``, then the same around the
+    feed-forward if the layer has one. Neither the outer norms nor the sums are taken here: a sublayer's output is left
+    pending on the stream together with the norm it has to pass, and the next norm kernel norms it, adds it into the
+    float32 residual and norms the sum for its own reader in one pass. A layer with a depth mix asks the stream for it
+    at its end (``ResidualStream.mix``), which the same kernel does."""
+
+    NORMS = ("mixer", "mixer_out", "feed_forward", "feed_forward_out")
+
+    def needed_norms(self):
+        return self.NORMS if self.feed_forward is not None else ("mixer", "mixer_out")
+
+    def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        h = self.norms["mixer"].add_norm(stream, ctx)
+        out, bias = self.mixer.forward(h, ctx, cache)
+        stream.add(out, bias, norm=self.norms["mixer_out"])
+        if self.feed_forward is not None:
+            h = self.norms["feed_forward"].add_norm(stream, ctx)
+            out, bias = self.feed_forward.forward(h, ctx)
+            stream.add(out, bias, norm=self.norms["feed_forward_out"])
+        if self.depth_mix is not None:
+            stream.mix(self.depth_mix.weights, self.depth_mix.index)

@@ -19,15 +19,17 @@ from .registry import register_embedding, register_head
 class TokenEmbedding(Embedding):
     graph_safe = True
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, name: Optional[str] = None):
+        """``name``: the table's full tensor name where it is not ``<prefix>.weight``."""
         self.prefix, self.vocab_size, self.hidden_size = prefix, int(vocab_size), int(hidden_size)
+        self.name = name or f"{prefix}.weight"
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {f"{self.prefix}.weight": ParamSpec((self.vocab_size, self.hidden_size))}
+        return {self.name: ParamSpec((self.vocab_size, self.hidden_size))}
 
     def load(self, get: TensorGetter) -> None:
-        self.weight = get(f"{self.prefix}.weight", "matrix").contiguous()
+        self.weight = get(self.name, "matrix").contiguous()
 
     def forward(self, ctx) -> torch.Tensor:
         out = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=ctx.device)
@@ -35,12 +37,43 @@ class TokenEmbedding(Embedding):
         return out
 
 
+@register_embedding("normed_token_embedding")
+class NormedTokenEmbedding(TokenEmbedding):
+    """A row gather followed by an RMS norm of the row with a weight of its own (``offset + w``), in one kernel."""
+
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, eps: float, offset: float = 0.0,
+                 name: Optional[str] = None, norm_name: Optional[str] = None):
+        super().__init__(prefix, vocab_size, hidden_size, name)
+        self.eps, self.offset = float(eps), float(offset)
+        self.norm_name = norm_name or f"{prefix}.norm.weight"
+        self.norm_weight: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = super().param_specs()
+        specs[self.norm_name] = ParamSpec((self.hidden_size,), role="vector", init="small" if self.offset else "norm")
+        return specs
+
+    def load(self, get: TensorGetter) -> None:
+        super().load(get)
+        self.norm_weight = (get(self.norm_name, "vector").float() + self.offset).contiguous()
+
+    def forward(self, ctx) -> torch.Tensor:
+        out = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=ctx.device)
+        kernels.embedding_norm(ctx.token_ids, self.weight, self.norm_weight, 0.0, self.eps, out)
+        return out
+
+
 @register_head("linear_head")
 class LinearHead(Head):
     graph_safe = True
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
+                 tied_name: Optional[str] = None, softcap: Optional[float] = None):
+        """``tied_to``: the prefix of the embedding whose table the head uses (``tied_name``: that table's full tensor
+        name where it is not ``<tied_to>.weight``). ``softcap``: logits become ``cap * tanh(logits / cap)``."""
         self.prefix, self.vocab_size, self.hidden_size, self.tied_to = prefix, int(vocab_size), int(hidden_size), tied_to
+        self.tied_name = tied_name or (f"{tied_to}.weight" if tied_to else None)
+        self.softcap = float(softcap) if softcap else None
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -50,11 +83,13 @@ class LinearHead(Head):
     def copies(self) -> Dict[str, str]:
         # The reference makes the head's parameter the embedding's own tensor when tie_word_embeddings is set
         # (models/qwen3/custom_builder.py:389-391), so a checkpoint it wrote holds the same values under both names.
-        return {f"{self.prefix}.weight": f"{self.tied_to}.weight"} if self.tied_to else {}
+        return {f"{self.prefix}.weight": self.tied_name} if self.tied_to else {}
 
     def load(self, get: TensorGetter) -> None:
-        name = f"{self.tied_to}.weight" if self.tied_to else f"{self.prefix}.weight"
-        self.weight = get(name, "matrix")
+        self.weight = get(self.tied_name if self.tied_to else f"{self.prefix}.weight", "matrix")
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return linear(x, self.weight, out_dtype=torch.float32)
+        logits = linear(x, self.weight, out_dtype=torch.float32)
+        if self.softcap is not None:
+            kernels.softcap(logits, self.softcap)
+        return logits

@@ -47,3 +47,34 @@ class SwiGLU(FeedForward):
             act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
             kernels.swiglu(gate_up, act)
         return pending_product(act, self.w_down), None
+
+
+@register_feed_forward("poly_norm_mlp")
+class PolyNormMLP(FeedForward):
+    """``down(act(up(x)))`` without gate and biases, with the PolyNorm activation: for a token's vector z of ``ff``
+    values, ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e`` with powers taken element by element, N(v) = v / sqrt(mean(v^2)
+    + eps) over the token's ff values, and the four learned numbers (a, b, c, e) in one tensor. The up product's result
+    and the three mean squares are float32; the activation is rounded once to the compute type for the down product,
+    whose result is float32."""
+
+    graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, eps: float):
+        self.prefix, self.hidden_size, self.intermediate_size, self.eps = prefix, int(hidden_size), int(intermediate_size), float(eps)
+        self.w_up = self.w_down = self.act = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        p, H, I = self.prefix, self.hidden_size, self.intermediate_size
+        return {f"{p}.up": ParamSpec((I, H)), f"{p}.down": ParamSpec((H, I)), f"{p}.act": ParamSpec((4,), role="vector", init="unit")}
+
+    def load(self, get: TensorGetter) -> None:
+        p = self.prefix
+        self.w_up = get(f"{p}.up", "matrix").contiguous()
+        self.w_down = get(f"{p}.down", "matrix").contiguous()
+        self.act = get(f"{p}.act", "vector").float().contiguous()
+
+    def forward(self, x, ctx):
+        z = linear(x, self.w_up, out_dtype=torch.float32)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.poly_norm(z, self.act, self.eps, act)
+        return linear(act, self.w_down, out_dtype=torch.float32), None

@@ -22,19 +22,27 @@ from .registry import register_norm
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, prefix: str, size: int, eps: float):
-        self.prefix, self.size, self.eps = prefix, int(size), float(eps)
+    def __init__(self, prefix: str, size: int, eps: float, offset: float = 0.0, name: Optional[str] = None):
+        """``offset``: the stored weight w stands for ``offset + w`` (1.0 for weights kept around zero); ``name``: the
+        tensor's full name where it is not ``<prefix>.weight``."""
+        self.prefix, self.size, self.eps, self.offset = prefix, int(size), float(eps), float(offset)
+        self.name = name or f"{prefix}.weight"
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {f"{self.prefix}.weight": ParamSpec((self.size,), role="vector", init="norm")}
+        return {self.name: ParamSpec((self.size,), role="vector", init="small" if self.offset else "norm")}
 
     def load(self, get: TensorGetter) -> None:
-        self.weight = get(f"{self.prefix}.weight", "vector").contiguous()
+        self.weight = get(self.name, "vector").contiguous()
+        if self.offset:
+            self.weight = (self.weight.float() + self.offset).contiguous()      # the factor itself, float32
 
     def add_norm(self, stream: ResidualStream, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         count = rows.numel() if rows is not None else stream.residual.shape[0]
         out = torch.empty((count, self.size), dtype=ctx.dtype, device=stream.residual.device)
+        if not stream.plain or (stream.pending is not None and stream.pending.dtype != ctx.dtype):
+            # the addend has a norm of its own or another type, or the layers' results are mixed: the general kernel
+            return stream.fold(self.weight, self.eps, out, rows)
         kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out,
                             delta_bias=stream.pending_bias, rows=rows)
         if rows is None:
@@ -44,7 +52,7 @@ class RMSNorm(Norm):
     def add_norm_deferred(self, stream: ResidualStream, ctx):
         """As ``add_norm`` for all rows, but a pending product of a decode step's few rows is added into the residual by
         its own kernel, which leaves the rows normalised but for their factors (``ScaledRows``) to the product after."""
-        product = stream.take_pending_product()
+        product = stream.take_pending_product() if stream.plain else None
         if product is None:
             return self.add_norm(stream, ctx)
         residual = stream.residual

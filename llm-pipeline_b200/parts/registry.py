@@ -14,7 +14,7 @@ from __future__ import annotations
 from typing import Callable, Dict
 
 _FAMILIES: Dict[str, Dict[str, type]] = {name: {} for name in (
-    "mixer", "feed_forward", "norm", "position", "block", "embedding", "head")}
+    "mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "depth_mix")}
 
 
 def _register(family: str, kind: str) -> Callable[[type], type]:
@@ -50,6 +50,10 @@ def register_embedding(kind: str):
 
 def register_head(kind: str):
     return _register("head", kind)
+
+
+def register_depth_mix(kind: str):
+    return _register("depth_mix", kind)
 
 
 def lookup(family: str, kind: str) -> type:

@@ -26,7 +26,7 @@ import sys
 from typing import Optional, Sequence
 
 PAGE_SIZE = 16          # tokens per page; divides the 64-token rounding of --max-tokens
-MAX_LIVE_REQUESTS = 64  # state slots (a trace keeps at most a handful of requests live)
+MAX_LIVE_REQUESTS = 4   # state slots: a trace keeps at most four requests live, so slots are used again
 
 
 def main(argv: Optional[Sequence[str]] = None, stdin=None, stdout=None) -> int:

@@ -49,7 +49,8 @@ class ParamSpec:
     """A tensor a part expects. ``role``: "matrix" (operand of a matrix product, kept in the
     compute type), "vector" (norm weight or bias: kept in float32 when stored so, else in the
     compute type), "table" (integers, kept as int32). ``optional`` tensors may be absent;
-    ``init`` tells the random-weights mode how to draw it ("normal" or "norm")."""
+    ``init`` tells the random-weights mode how to draw it ("normal": N(0, std); "norm": around one; "small": around
+    zero; "average": around 1 / n over the last axis; "unit": of order one)."""
 
     shape: Tuple[int, ...]
     role: str = "matrix"
@@ -155,7 +156,16 @@ class RandomSource(WeightSource):
         if spec.role == "table":
             return torch.zeros(spec.shape, dtype=torch.int32, device=self.device)
         noise = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=self.device)
-        value = noise.mul_(0.1).add_(1.0) if spec.init == "norm" else noise.mul_(self.std)
+        if spec.init == "norm":
+            value = noise.mul_(0.1).add_(1.0)
+        elif spec.init == "small":               # a weight kept around zero (it stands for 1 + w), a bias
+            value = noise.mul_(0.1)
+        elif spec.init == "average":             # weights of a weighted sum over the last axis: about 1 / n each
+            value = noise.mul_(0.1).add_(1.0).div_(max(1, spec.shape[-1]))
+        elif spec.init == "unit":                # coefficients of order one
+            value = noise.mul_(0.25).add_(0.5)
+        else:
+            value = noise.mul_(self.std)
         return value.to(self.dtype)
 
 
