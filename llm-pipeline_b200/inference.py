@@ -268,10 +268,13 @@ class Qwen3InferenceEngine:
         """Sizes and parameter counts from the model's configuration (models/qwen3/factory.py:132-166)."""
         c = self.model_config
         info = {"model_type": getattr(c, "model_type", "qwen3"), "vocab_size": c.vocab_size, "hidden_size": c.hidden_size,
-                "num_layers": c.num_hidden_layers, "num_attention_heads": c.num_attention_heads,
-                "num_key_value_heads": c.num_key_value_heads, "intermediate_size": c.intermediate_size,
-                "max_position_embeddings": c.max_position_embeddings, "head_dim": c.head_dim,
-                "torch_dtype": str(self.engine.dtype), "use_cache": True, "tie_word_embeddings": bool(c.tie_word_embeddings)}
+                "num_layers": c.num_hidden_layers, "max_position_embeddings": c.max_position_embeddings,
+                "torch_dtype": str(self.engine.dtype), "use_cache": True}
+        # sizes that only some architectures have (every layer of the Qwen3 decoder has the same heads; a hybrid has none to name)
+        for key in ("num_attention_heads", "num_key_value_heads", "intermediate_size", "head_dim"):
+            if hasattr(c, key):
+                info[key] = getattr(c, key)
+        info["tie_word_embeddings"] = bool(getattr(c, "tie_word_embeddings", self.engine.model.spec.head.args.get("tied_to") is not None))
         info.update(c.parameter_counts())
         return info
 
@@ -300,3 +303,8 @@ class Qwen3InferenceEngine:
         self.engine._requests.clear()
         self._continuous.clear()
         self._continuous_done.clear()
+
+
+# The entry point serves every registered architecture (``config.json`` chooses the model class); these names say so.
+InferenceConfig = Qwen3InferenceConfig
+InferenceEngine = Qwen3InferenceEngine
