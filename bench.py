@@ -595,6 +595,162 @@ def run_ours(args):
     return 0 if check is None or check["ok"] else 1
 
 
+# ---- another design beside the closest existing one ------------------------------------------------------------------
+# ``--compare zupilorn``: prefill (one 2,048-token prompt) and decode (batch 8, 2,048 tokens of context) of the Zupilorn
+# hybrid decoder (recurrent and latent-attention mixers, PolyNorm and routed-expert feed-forwards) at layer sizes of real
+# models, beside a Qwen3 dense decoder of the same width, depth and vocabulary on the same GPU, with the device time of
+# every kernel class and, where the work of a class is known in closed form, what it achieved over the measured peak.
+ZUPILORN_SIZES = {
+    "1k": {"width": 1024, "gru": 2048, "ff": 4096, "heads": 8, "dim": 64, "rot": 32, "vdim": 64, "rank": 256,
+           "experts": 16, "top": 2, "expert_ff": 1024, "layers": 4, "vocab": 32000, "qwen_heads": (8, 4)},
+    "2k": {"width": 2048, "gru": 4096, "ff": 8192, "heads": 16, "dim": 128, "rot": 64, "vdim": 128, "rank": 512,
+           "experts": 32, "top": 4, "expert_ff": 1408, "layers": 4, "vocab": 32000, "qwen_heads": (16, 8)},
+}
+
+
+def zupilorn_config(z):
+    layers = []
+    for i in range(z["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "mingru", "mixer": {"width": z["gru"]}, "mlp": {"kind": "dense", "ff": z["ff"]}})
+        else:
+            layers.append({"type": "latent_attention",
+                           "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
+                                     "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["rot"]}},
+                           "mlp": {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+                                   "router": {"experts": z["experts"], "top": z["top"]}}})
+    return {"architecture": "Zupilorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": layers}
+
+
+def qwen_config_like(z):
+    heads, kv = z["qwen_heads"]
+    return {**QWEN3_8B, "num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": heads,
+            "num_key_value_heads": kv, "head_dim": 128, "intermediate_size": z["ff"], "vocab_size": z["vocab"]}
+
+
+def zupilorn_work(z, tokens, keys_per_token, decode):
+    """Closed-form work of the design's own kernel classes for one step: label -> (bytes, flops). ``tokens`` rows in the
+    step, each seeing ``keys_per_token`` keys on average."""
+    D, L = z["width"], z["layers"]
+    gru_layers, att_layers = (L + 1) // 2, L // 2
+    dk = z["rank"] + z["rot"]
+    work = {}
+    # per layer three folds of the stream (before the mixer, between, and with the depth mix at the next reader)
+    mix_reads = sum(i + 1 for i in range(L))
+    work["add_norm_mix"] = (tokens * D * (3 * L * (4 + 4 + 4 + 2) + 4 * mix_reads + 4 * L), 0.0)
+    work["min_gru"] = (gru_layers * tokens * z["gru"] * ((12 if decode else 24) + 2), 0.0)
+    work["poly_norm"] = (gru_layers * tokens * z["ff"] * (4 + 4 + 2), 0.0)
+    if decode:
+        work["latent_attention_mma"] = (att_layers * tokens * keys_per_token * dk * 2, 0.0)
+    else:
+        work["latent_attention_mma"] = (0.0, att_layers * 2.0 * tokens * keys_per_token * z["heads"] * (dk + z["rank"]))
+    pairs = tokens * z["top"]
+    expert_weights = 3 * z["expert_ff"] * D * 2
+    if decode:
+        work["expert_rows"] = (att_layers * pairs * expert_weights, 0.0)
+    else:
+        work["expert_rows"] = (0.0, att_layers * 2.0 * pairs * 3 * z["expert_ff"] * D)
+    work["routed_experts_grouped"] = work["expert_rows"]
+    return work
+
+
+def qwen_work(cfg, tokens, keys_per_token, decode):
+    D, L, I = cfg["hidden_size"], cfg["num_hidden_layers"], cfg["intermediate_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    work = {"add_rmsnorm": (tokens * D * (2 * L + 1) * (4 + 4 + 2 + 2), 0.0), "swiglu": (L * tokens * I * 6, 0.0),
+            "qkv_post": (L * tokens * (nq + 2 * nkv) * d * 6, 0.0)}
+    if decode:
+        work["decode_attention"] = (L * tokens * keys_per_token * 2 * nkv * d * 2, 0.0)
+    else:
+        work["paged_attention"] = (0.0, L * 4.0 * tokens * keys_per_token * nq * d)
+    return work
+
+
+def compare_one(cfg_json, work_of, peak, args, label=None):
+    import torch
+
+    from llm_pipeline_b200.config import resolve_config
+    from llm_pipeline_b200.engine import StepEntry
+    from llm_pipeline_b200.engine.generate import GenerationEngine
+    from llm_pipeline_b200.models import build_model
+    from llm_pipeline_b200.ops import build_library
+    from llm_pipeline_b200.ops.timing import KernelTimes
+    from llm_pipeline_b200.weights import random_tensors
+
+    build_library()
+    config = resolve_config(cfg_json)
+    model = build_model(config)
+    model.load(random_tensors(config, seed=0, dtype=torch.bfloat16, device="cuda:0"), torch.device("cuda:0"), torch.bfloat16)
+    room = -(-(CONTEXT + 64 + args.warmup + args.steps) // 256) * 256
+    engine = GenerationEngine(model, config, page_size=PAGE_SIZE, num_pages=(args.batch + 1) * (room // PAGE_SIZE),
+                              max_num_seqs=args.batch + 1, max_num_batched_tokens=PREFILL_TOKENS, max_model_len=room)
+    out = {}
+    prefill_ms = time_prefill(engine, PREFILL_TOKENS, repeats=3, warmup=3)
+    out["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3), "tok_s": round(PREFILL_TOKENS * 1e3 / prefill_ms, 1)}
+    dec = time_decode(engine, args.batch, args.steps, args.warmup, seed=7, e2e=False)
+    out["decode"] = {"batch": args.batch, "context": CONTEXT, "ms_per_step": round(dec["ms"], 4), "tok_s": round(dec["tok_s"], 1)}
+
+    def kernel_table(entries_of, work, release):
+        runner = engine.runner
+        graphs, runner.use_graphs = runner.use_graphs, False
+        try:
+            runner.step(entries_of(0))
+            torch.cuda.synchronize()
+            times = KernelTimes(label)
+            torch.cuda._sleep(int(1.5e8))
+            with times:
+                runner.step(entries_of(1))
+            torch.cuda.synchronize()
+        finally:
+            runner.use_graphs = graphs
+            for rid in release:
+                runner.release(rid)
+        table = times.table()
+        total = sum(e["us"] for e in table.values())
+        rows = {}
+        for name, e in table.items():
+            row = {"launches": e["launches"], "us": round(e["us"], 1), "share": round(e["us"] / total, 3)}
+            nbytes, flops = work.get(name, (e["bytes"] if e["rows"] and e["rows"] <= 64 else 0.0, e["flops"] if e["rows"] > 64 else 0.0))
+            seconds = e["us"] * 1e-6
+            if nbytes:
+                row["gbs"] = round(nbytes / seconds / 1e9, 1)
+                row["frac_hbm"] = round(nbytes / seconds / 1e9 / peak["hbm_gbs"], 3)
+            elif flops:
+                row["tflops"] = round(flops / seconds / 1e12, 1)
+                row["frac_bf16_burst"] = round(flops / seconds / 1e12 / peak["bf16_tflops_burst"], 3)
+            rows[name] = row
+        return {"kernel_us": round(total, 1), "classes": rows}
+
+    vocab = model.spec.vocab_size
+    prompts = random_prompts(vocab, 2, PREFILL_TOKENS, 900)
+    if not args.lean:
+        out["prefill"]["kernels"] = kernel_table(lambda k: [StepEntry(f"p{k}", prompts[k], [PREFILL_TOKENS - 1])],
+                                                 work_of(PREFILL_TOKENS, (PREFILL_TOKENS + 1) / 2, False), ("p0", "p1"))
+        ids = [f"d{i}" for i in range(args.batch)]
+        contexts = random_prompts(vocab, args.batch, CONTEXT - 2, 901)
+        for rid, prompt in zip(ids, contexts):
+            engine.runner.step([StepEntry(rid, prompt, [])])
+        out["decode"]["kernels"] = kernel_table(lambda k: [StepEntry(rid, [5 + k], [0]) for rid in ids],
+                                                work_of(args.batch, CONTEXT, True), ids)
+    del engine, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_compare(args):
+    peak = peaks()
+    z = ZUPILORN_SIZES[args.size]
+    clocks = ClockSampler()
+    clocks.start()
+    ours = compare_one(zupilorn_config(z), lambda n, k, d: zupilorn_work(z, n, k, d), peak, args)
+    qcfg = qwen_config_like(z)
+    beside = compare_one(qcfg, lambda n, k, d: qwen_work(qcfg, n, k, d), peak, args, product_labels(qcfg))
+    print(json.dumps({"compare": "zupilorn", "size": args.size, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+                      "sizes": z, "zupilorn": ours, "qwen3_same_width_and_depth": beside, "peaks": peak, "clocks": clocks.stop()}))
+    return 0
+
+
 def run_reference(args):
     """The reference's own model class and cache loop, unmodified, from baseline/_ref."""
     ref_root = os.path.join(ROOT, "baseline", "_ref")
@@ -679,6 +835,10 @@ def main() -> int:
     parser.add_argument("--lean", action="store_true", help="leave out the per-kernel breakdown, the page-size point, the plain "
                         "PyTorch baseline and the self-check")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
+    parser.add_argument("--compare", default="", choices=("", "zupilorn"),
+                        help="instead of the headline: prefill and decode of this design at real layer sizes beside a Qwen3 dense "
+                        "decoder of the same width and depth, with the time of every kernel class")
+    parser.add_argument("--size", default="2k", choices=tuple(ZUPILORN_SIZES), help="with --compare: the layer sizes")
     args = parser.parse_args()
     globals()["PAGE_SIZE"] = args.page_size
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
@@ -686,6 +846,8 @@ def main() -> int:
             print("bench.py measures a single-GPU engine: run it with --gpus 1 (no multi-GPU path is built)")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.compare:
+        return run_compare(args)
     if args.impl == "plain":
         name, cfg = SHAPES[args.shape]
         out = plain_baseline(cfg, args.layers or cfg["num_hidden_layers"], CONTEXT)

@@ -65,6 +65,8 @@ _SIGNATURES = {
     "llmp_min_gru": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P],
     "llmp_latent_kv_post": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _F, _P, _P, _I, _P, _P, _I, _P],
     "llmp_latent_attention": [_P, _L, _L, _P, _L, _L, _P, _I, _P, _I, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P],
+    "llmp_latent_attention_mma": [_P, _L, _L, _P, _L, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I, _F, _I,
+                                  _I, _P, _P],
     "llmp_route_topk": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _P],
     "llmp_expert_rows": [_P, _P, _P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P],
 }
@@ -912,3 +914,50 @@ def routed_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tenso
                    limit: float, out: torch.Tensor) -> torch.Tensor:
     """The experts' work for a step's rows, by the kernel that suits their number (``expert_rows`` for few)."""
     return expert_rows(h, w_gate_up, w_down, ids, weights, limit, out)
+
+
+LATENT_SEGMENT_KEYS = 256            # keys per segment when a step's rows are too few to fill the GPU (a multiple of the key tile)
+
+
+def latent_mma_supports(dtype: torch.dtype, rank: int, rot: int, page_size: int) -> bool:
+    """Whether the tensor-core latent attention kernel serves these sizes (bfloat16, sizes in multiples of 16)."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = library().llmp_latent_mma_supports
+    fn.argtypes = [_I, _I, _I]
+    fn.restype = _I
+    return bool(fn(rank, rot, page_size))
+
+
+def latent_mma_tokens_per_tile(num_heads: int) -> int:
+    fn = library().llmp_latent_mma_tokens_per_tile
+    fn.argtypes = [_I]
+    fn.restype = _I
+    return int(fn(num_heads))
+
+
+def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, q_start: torch.Tensor,
+                         ctx_len: torch.Tensor, positions: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor,
+                         out: torch.Tensor, scale: float, segments: int = 0) -> torch.Tensor:
+    """``latent_attention`` on the tensor cores for bfloat16. ``tile_req``/``tile_tok0``: the work list (request and
+    first token of every tile of ``latent_mma_tokens_per_tile`` tokens). ``segments`` > 0: the keys are cut into that many
+    segments of ``LATENT_SEGMENT_KEYS``, each with blocks of its own, and a second kernel adds them up (for steps of few
+    rows over long contexts; ``segments`` must cover the longest context)."""
+    N, H, rank = q_lat.shape
+    rot = q_rot.shape[2]
+    _need(q_lat.dtype == torch.bfloat16 and q_rot.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
+          "latent_attention_mma takes bfloat16")
+    _need(q_rot.shape[:2] == (N, H) and out.shape == (N, H, rank) and q_lat.stride(2) == 1 and out.stride(2) == 1 and
+          (rot == 0 or q_rot.stride(2) == 1), "latent attention shapes do not match")
+    _need(pages.is_contiguous() and pages.dim() == 3 and pages.shape[2] == rank + rot, "latent pages have the wrong layout")
+    for t, name in ((tables, "tables"), (q_start, "q_start"), (ctx_len, "ctx_len"), (positions, "positions"), (tile_req, "tile_req"),
+                    (tile_tok0, "tile_tok0")):
+        _i32(t, name)
+    scratch = None
+    if segments > 0:
+        scratch = torch.empty(segments * N * H * (rank + 2), dtype=torch.float32, device=q_lat.device)
+    _call("llmp_latent_attention_mma", _ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1),
+          _ptr(pages), _ptr(tables), tables.shape[1], _ptr(q_start), _ptr(ctx_len), _ptr(positions), _ptr(tile_req), _ptr(tile_tok0),
+          tile_req.numel(), _ptr(out), out.stride(0), out.stride(1), N, H, rank, rot, pages.shape[1], float(scale),
+          LATENT_SEGMENT_KEYS if segments > 0 else 0, int(segments), _ptr(scratch), _stream())
+    return out

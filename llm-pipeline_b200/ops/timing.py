@@ -65,8 +65,8 @@ class KernelTimes:
         self._depth += 1
         if self._depth > 1:
             return self
-        self._saved = (kernels._call, torch.mm, kernels.library_add_product)
-        call_before, mm_before, add_before = self._saved
+        self._saved = (kernels._call, torch.mm, kernels.library_add_product, torch.bmm)
+        call_before, mm_before, add_before, bmm_before = self._saved
         outer = self
 
         def timed(label, work, fn, *args, **kwargs):
@@ -97,14 +97,19 @@ class KernelTimes:
             label = outer._label("mm+residual", work) if outer._label else "mm into the residual (library)"
             return timed(label, work, add_before, residual, x, w)
 
-        kernels._call, torch.mm, kernels.library_add_product = call, mm, add_product
+        def bmm(a, b, **kwargs):
+            # the library's batched product (one product per head): a is [B, M, K], b is [B, K, N]
+            work = (a.shape[0] * a.shape[1], b.shape[2], a.shape[2])
+            return timed(outer._label("bmm", work) if outer._label else "bmm (library)", work, bmm_before, a, b, **kwargs)
+
+        kernels._call, torch.mm, kernels.library_add_product, torch.bmm = call, mm, add_product, bmm
         return self
 
     def __exit__(self, *exc):
         from . import kernels
         self._depth -= 1
         if self._depth == 0:
-            kernels._call, torch.mm, kernels.library_add_product = self._saved
+            kernels._call, torch.mm, kernels.library_add_product, torch.bmm = self._saved
             self._saved = None
 
     # -- results -----------------------------------------------------------------------------

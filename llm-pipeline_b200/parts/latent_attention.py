@@ -27,6 +27,7 @@ from ..cache.spec import TokenPagesSpec
 from ..ops import kernels
 from ..ops.linear import batched_linear, linear
 from ..weights.source import ParamSpec
+from .attention import AttentionPolicy
 from .base import LayerCache, Mixer, TensorGetter
 from .registry import register_mixer
 
@@ -70,6 +71,40 @@ class LatentAttention(Mixer):
         self.w_uv = get(f"{p}.uv", "matrix").view(H, self.vdim, self.kv_rank).contiguous()
         self.w_o = get(f"{p}.o", "matrix").contiguous()
 
+    # Blocks per SM below which a step's tiles are too few and the keys are cut into segments with blocks of their own
+    # (decode steps, short portions over long contexts); and the context from which that is worth a second kernel.
+    SEGMENTS_BELOW_BLOCKS_PER_SM = 2.0
+    SEGMENTS_MIN_CONTEXT = 2 * kernels.LATENT_SEGMENT_KEYS
+
+    def attend(self, ctx, q_lat, q_rot, out, cache: LayerCache) -> None:
+        """Attention of the step's rows over the cache: the tensor-core kernel for bfloat16 where it serves the sizes,
+        else the general kernel (float32, sizes that are no multiples of 16)."""
+        tables = ctx.block_tables[cache.group]
+        if not kernels.latent_mma_supports(q_lat.dtype, self.kv_rank, self.rot_dim, cache.pages.shape[1]) or self.dim % 8 or self.rot_dim % 8:
+            kernels.latent_attention(q_lat, q_rot, cache.pages, tables, ctx.token_request, ctx.positions, out, self.scale)
+            return
+        per_tile = kernels.latent_mma_tokens_per_tile(self.num_heads)
+        key = ("latent_attention_tiles", per_tile)
+        tiles = ctx.memo.get(key)
+        if tiles is None:
+            if ctx.max_q_len == 1:
+                # one token a request: tile r is request r (made on the device, so that a captured step holds no copy from the host)
+                tiles = (torch.arange(ctx.num_requests, dtype=torch.int32, device=ctx.device),
+                         torch.zeros(ctx.num_requests, dtype=torch.int32, device=ctx.device))
+            else:
+                req, tok0, _seg, _slot, _places = AttentionPolicy.plan_items(ctx.starts, ctx.q_lens, per_tile, 0, 1, 1, kernels.sm_count())
+                host = torch.tensor([req, tok0], dtype=torch.int32).pin_memory()
+                dev = host.to(ctx.device, non_blocking=True)
+                tiles = (dev[0].contiguous(), dev[1].contiguous())
+            ctx.memo[key] = tiles
+        longest = ctx.decode_ctx_bound or ctx.max_ctx_len
+        blocks = tiles[0].numel() * -(-self.num_heads // 16) * -(-self.kv_rank // 128)
+        segments = 0
+        if blocks < self.SEGMENTS_BELOW_BLOCKS_PER_SM * kernels.sm_count() and longest >= self.SEGMENTS_MIN_CONTEXT:
+            segments = -(-longest // kernels.LATENT_SEGMENT_KEYS)
+        kernels.latent_attention_mma(q_lat, q_rot, cache.pages, tables, ctx.q_start, ctx.ctx_len, ctx.positions, tiles[0], tiles[1],
+                                     out, self.scale, segments)
+
     def forward(self, x, ctx, cache: LayerCache):
         if cache.pages is None or cache.group is None:
             raise RuntimeError("the latent attention mixer needs the pages of its cache")
@@ -84,8 +119,7 @@ class LatentAttention(Mixer):
         q_lat = torch.empty((N, H, rank), dtype=x.dtype, device=x.device)
         batched_linear(q[:, :, :self.dim].transpose(0, 1), self.w_uk_t, q_lat.transpose(0, 1))
         mixed = torch.empty((N, H, rank), dtype=x.dtype, device=x.device)
-        kernels.latent_attention(q_lat, q[:, :, self.dim:], cache.pages, ctx.block_tables[cache.group], ctx.token_request,
-                                 ctx.positions, mixed, self.scale)
+        self.attend(ctx, q_lat, q[:, :, self.dim:], mixed, cache)
         values = torch.empty((N, H, self.vdim), dtype=x.dtype, device=x.device)
         batched_linear(mixed.transpose(0, 1), self.w_uv, values.transpose(0, 1))
         return linear(values.view(N, H * self.vdim), self.w_o, out_dtype=torch.float32), None

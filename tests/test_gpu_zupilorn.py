@@ -224,6 +224,37 @@ def test_far_keys_page_borders_and_first_tokens_under_a_sharp_softmax(tmp_path, 
     Z.assert_matches(H.replay(runner, H.cut_mixed(requests, (page, 2, page + 1), max_live=3, decode_tail=page + 3)), want, dtype, "sharp: mixed", tol_share)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_few_rows_over_long_contexts_take_key_segments(tmp_path, dtype):
+    """Contexts of several segments of keys, sharp softmax: decoding steps and short portions cut the keys into
+    segments with blocks of their own (bfloat16), whose sums a second kernel adds; positions around segment borders."""
+    from llm_pipeline_b200.ops import kernels
+    cfg, W, folder = case(tmp_path, "wide_latent", 8, sharp=5.0)
+    seg = kernels.LATENT_SEGMENT_KEYS
+    requests = requests_for(cfg, [2 * seg + 40, 3 * seg + 2, 70], 700)
+    want = Z.oracle(cfg, W, requests)
+    runner = H.make_runner(folder, dtype, page_size=16, num_pages=120, max_request_tokens=3 * seg + 16, max_requests=3)
+    used = []
+    launch = kernels.latent_attention_mma
+
+    def counting(*args, **kwargs):
+        used.append(args[-1] if not kwargs else kwargs.get("segments", args[-1]))
+        return launch(*args, **kwargs)
+
+    kernels.latent_attention_mma = counting
+    try:
+        share = 1.0 if dtype == torch.float32 else 0.97
+        Z.assert_matches(H.replay(runner, H.cut_tail_one_by_one(requests, tail=seg + 70)), want, dtype, "segments: decoding", share)
+        Z.assert_matches(H.replay(runner, H.cut_portions(requests, (seg - 3, 2, 5, seg + 7, 3))), want, dtype, "segments: portions", share)
+        Z.assert_matches(H.replay(runner, H.cut_mixed(requests, (seg, 2, 9), max_live=3, decode_tail=40)), want, dtype, "segments: mixed", share)
+    finally:
+        kernels.latent_attention_mma = launch
+    if dtype == torch.bfloat16:
+        assert any(n > 1 for n in used) and any(n == 0 for n in used), "both forms of the tensor-core kernel should have run"
+    else:
+        assert not used
+
+
 def test_long_decoding_through_replayed_graphs(tmp_path):
     cfg, W, folder = case(tmp_path, "hybrid", 6)
     requests = requests_for(cfg, [260, 231], 400)

@@ -56,6 +56,10 @@ CONFIGS: Dict[str, dict] = {
                               width=88, vocab=130, eps=3e-6, softcap=30.0),
     "dense_only": config([latent_layer(5, 8, 8, 8, 64, dense(72), base=1000.0), mingru_layer(64, dense(64)),
                           latent_layer(2, 40, 24, 12, 72, dense(40), scale=0.2)], width=64, vocab=97),
+    # latents and rotated parts in multiples of 16 (the sizes of the tensor-core attention kernel in bfloat16): more heads
+    # than a tile's 16, a latent of more than one chunk of 128 value columns, and one of a single 16
+    "wide_latent": config([latent_layer(20, 16, 16, 16, 160, dense(64)), mingru_layer(48, None),
+                           latent_layer(6, 32, 32, 24, 64, dense(48)), latent_layer(3, 8, 16, 8, 16, None)], width=80, vocab=120),
     "experts_only": config([mingru_layer(48, moe(9, 3, 24, limit=3.0)), latent_layer(2, 16, 8, 16, 32, moe(4, 4, 40))],
                            width=56, vocab=150, softcap=4.0),
 }
