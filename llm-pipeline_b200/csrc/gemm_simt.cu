@@ -92,6 +92,38 @@ LLMP_API int llmp_gemm_simt(const void* A, const void* W, const void* bias, int 
     return llmp_check_launch("gemm_simt");
 }
 
+// The same batch for at most 16 rows a product (a decode step): a warp per output column reads the column's weight
+// row once and keeps one sum per row of A; the K products of a sum are added lane by lane in ascending k, then across
+// the lanes in a fixed order.
+#define GR_MAX_ROWS 16
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+gemm_rows_kernel(const TI* __restrict__ A, const TI* __restrict__ W, TO* __restrict__ C, int M, int N, int K, long lda, long ldw,
+                 long ldc, long batch_a, long batch_w, long batch_c) {
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= N) return;
+    A += (size_t)blockIdx.y * batch_a;
+    C += (size_t)blockIdx.y * batch_c;
+    const TI* w = W + (size_t)blockIdx.y * batch_w + (size_t)n * ldw;
+    float acc[GR_MAX_ROWS];
+#pragma unroll
+    for (int m = 0; m < GR_MAX_ROWS; ++m) acc[m] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+        const float wv = to_float(w[k]);
+#pragma unroll
+        for (int m = 0; m < GR_MAX_ROWS; ++m)
+            if (m < M) acc[m] = fmaf(to_float(A[(size_t)m * lda + k]), wv, acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < GR_MAX_ROWS; ++m) {
+        if (m < M) {
+            const float v = warp_sum(acc[m]);
+            if (lane == 0) C[(size_t)m * ldc + n] = from_float<TO>(v);
+        }
+    }
+}
+
 // A batch of such products in one launch: product b reads A + b * batch_a and W + b * batch_w and writes C + b * batch_c
 // (strides in elements; rows of any of them may lie further apart than they are long, so one product per head
 // can read and write the heads of a [tokens, heads, size] tensor in place).
@@ -101,6 +133,23 @@ LLMP_API int llmp_gemm_simt_batched(const void* A, const void* W, void* C, int i
     if (M <= 0 || N <= 0 || batch <= 0) return 0;
     LLMP_REQUIRE(K > 0, "batched gemm: bad K %d", K);
     LLMP_REQUIRE((M + GT_BM - 1) / GT_BM <= 65535 && batch <= 65535, "batched gemm: too many rows %d or products %d", M, batch);
+    if (M <= GR_MAX_ROWS && (N + 7) / 8 <= 65535) {
+        dim3 rows_grid((N + 7) / 8, batch);
+        if (in_dtype == LLMP_F32 && out_dtype == LLMP_F32)
+            gemm_rows_kernel<float, float><<<rows_grid, 256, 0, stream>>>((const float*)A, (const float*)W, (float*)C, M, N, K, lda, ldw,
+                                                                          ldc, batch_a, batch_w, batch_c);
+        else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_BF16)
+            gemm_rows_kernel<bf16, bf16><<<rows_grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc,
+                                                                        batch_a, batch_w, batch_c);
+        else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_F32)
+            gemm_rows_kernel<bf16, float><<<rows_grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc,
+                                                                         batch_a, batch_w, batch_c);
+        else {
+            llmp_set_error("batched gemm: unsupported type combination in=%d out=%d", in_dtype, out_dtype);
+            return 1;
+        }
+        return llmp_check_launch("gemm_simt_batched (rows)");
+    }
     dim3 grid((N + GT_BN - 1) / GT_BN, (M + GT_BM - 1) / GT_BM, batch);
     if (in_dtype == LLMP_F32 && out_dtype == LLMP_F32)
         gemm_nt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)A, (const float*)W, nullptr, 0, (float*)C, M, N, K,

@@ -3,18 +3,19 @@
 // the key, its first `rank` entries are the value.
 //
 // A block takes a tile of 64 rows (consecutive tokens of one request, the head running fastest, so the key tile it
-// streams serves every head), one chunk of 128 value columns, and, in a step whose requests bring few tokens over long
-// contexts, one segment of the keys. Each of the four warps owns 16 rows with their running softmax and output chunk
-// in registers. Keys are walked in tiles of 64 aligned to key 0 (the same operations for a row however the prompt was
-// cut), copied from the pages with 16-byte cp.async; the key tile in shared memory is also the value tile. With
+// streams serves every head), one chunk of value columns (128, or 256 for latents above 128), and, in a step whose
+// requests bring few tokens over long contexts, one segment of the keys. Eight warps: warp w owns the 16 rows of row
+// group w & 3 and, of every 64-key tile, the 32 keys of half w >> 2, with a running softmax and output chunk of its
+// own in registers; at the end the two warps of a row group add their sums in shared memory, first half first. A warp
+// whose rows do not exist (a decode step fills 16 of the 64 rows or fewer) only helps with the copies. Keys are walked in tiles of 64 aligned to key 0 (the same
+// operations for a row however the prompt was cut), copied from the pages with 16-byte cp.async; the key tile in shared memory is also the value tile. With
 // segments, a block leaves its unnormalised sums, maximum and row sum in scratch and a second kernel adds the segments
 // of a row in ascending order (segments are fixed ranges of key indices, so this too is the same for every step).
 #include "common.cuh"
 
 #define LM_ROWS 64
 #define LM_KEYS 64
-#define LM_THREADS 128
-#define LM_VCHUNK 128
+#define LM_THREADS 256
 
 struct LatentMmaParams {
     const bf16* q_lat; long ql_t, ql_h;
@@ -63,7 +64,8 @@ __device__ __forceinline__ unsigned lm_pack(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
-__global__ void __launch_bounds__(LM_THREADS, 2) latent_attention_mma_kernel(const LatentMmaParams p) {
+template <int LM_VCHUNK>
+__global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(const LatentMmaParams p) {
     extern __shared__ __align__(16) unsigned char lm_smem[];
     __shared__ long long key_off[LM_KEYS];
     const int dk = p.rank + p.rot;
@@ -75,6 +77,7 @@ __global__ void __launch_bounds__(LM_THREADS, 2) latent_attention_mma_kernel(con
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int rg = warp & 3, half = warp >> 2;                  // row group and key half of this warp
     // later tiles of a prompt see more keys: the blocks of the last tile start first
     const int tile = p.num_tiles - 1 - (int)(blockIdx.x / (unsigned)p.head_chunks);
     const int hc = (int)(blockIdx.x % (unsigned)p.head_chunks);
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(LM_THREADS, 2) latent_attention_mma_kernel(con
     int row_pos[2];
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
-        const int row = warp * 16 + g + 8 * h2;
+        const int row = rg * 16 + g + 8 * h2;
         const int tl = row / hpc, h = row % hpc;
         row_pos[h2] = (tl < ntok && h < heads) ? pos0 + tok0 + tl : -1;
     }
@@ -131,11 +134,12 @@ __global__ void __launch_bounds__(LM_THREADS, 2) latent_attention_mma_kernel(con
     float l_run[2] = {0.f, 0.f};
 
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    const int warp_last_tok = (warp * 16 + 15) / hpc;
+    const int warp_last_tok = (rg * 16 + 15) / hpc;
     const int warp_hi_pos = pos0 + tok0 + (warp_last_tok < ntok ? warp_last_tok : ntok - 1);
-    const int warp_first_tok = (warp * 16) / hpc;
+    const int warp_first_tok = (rg * 16) / hpc;
+    const bool warp_has_rows = warp_first_tok < ntok;
     const int warp_lo_pos = pos0 + tok0 + (warp_first_tok < ntok ? warp_first_tok : ntok - 1);
-    const bf16* Qw = Qs + (size_t)(warp * 16 + (lane & 15)) * STRIDE + (lane >> 4) * 8;
+    const bf16* Qw = Qs + (size_t)(rg * 16 + (lane & 15)) * STRIDE + (lane >> 4) * 8;
     for (int j0 = (lo / LM_KEYS) * LM_KEYS; j0 <= hi; j0 += LM_KEYS) {
         if (tid < LM_KEYS) {
             const int j = j0 + tid;
@@ -155,10 +159,9 @@ __global__ void __launch_bounds__(LM_THREADS, 2) latent_attention_mma_kernel(con
         asm volatile("cp.async.commit_group;\n" ::: "memory");
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         __syncthreads();
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        do {
             const int jh = j0 + half * 32;
-            if (jh > warp_hi_pos || jh > hi) continue;       // every row of this warp lies before these keys
+            if (!warp_has_rows || jh > warp_hi_pos || jh > hi) break;      // no row of this warp sees these keys
             float s[4][4];
 #pragma unroll
             for (int nb = 0; nb < 4; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(LM_THREADS, 2) latent_attention_mma_kernel(con
                     }
                 }
             }
-        }
+        } while (false);
         __syncthreads();                                         // the tile's buffer may be overwritten now
     }
 
@@ -246,10 +249,44 @@ __global__ void __launch_bounds__(LM_THREADS, 2) latent_attention_mma_kernel(con
         l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 1);
         l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 2);
     }
+    // The two halves of a row group meet: the second half's warp leaves its maximum, row sum and sums in shared memory
+    // (the query and key tiles are no longer read), the first half's warp adds them to its own and stores.
+    {
+        float* xo = reinterpret_cast<float*>(lm_smem);            // [4 row groups][32 lanes][LM_VCHUNK / 2 + 4]
+        constexpr int PER_LANE = LM_VCHUNK / 2 + 4;
+        float* mine = xo + ((size_t)rg * 32 + lane) * PER_LANE;
+        if (half == 1) {
+#pragma unroll
+            for (int i = 0; i < LM_VCHUNK / 8; ++i)
+                *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
+            *reinterpret_cast<float4*>(mine + LM_VCHUNK / 2) = make_float4(m_run[0], m_run[1], l_run[0], l_run[1]);
+        }
+        __syncthreads();
+        if (half == 1) return;
+        const float4 other = *reinterpret_cast<const float4*>(mine + LM_VCHUNK / 2);
+        const float om[2] = {other.x, other.y}, ol[2] = {other.z, other.w};
+        float wa[2], wb[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const float m = fmaxf(m_run[h2], om[h2]);
+            wa[h2] = (m_run[h2] > -INFINITY) ? lm_ex2(m_run[h2] - m) : 0.f;
+            wb[h2] = (om[h2] > -INFINITY) ? lm_ex2(om[h2] - m) : 0.f;
+            l_run[h2] = l_run[h2] * wa[h2] + ol[h2] * wb[h2];
+            m_run[h2] = m;
+        }
+#pragma unroll
+        for (int i = 0; i < LM_VCHUNK / 8; ++i) {
+            const float4 x = *reinterpret_cast<const float4*>(mine + 4 * i);
+            o[i][0] = o[i][0] * wa[0] + x.x * wb[0];
+            o[i][1] = o[i][1] * wa[0] + x.y * wb[0];
+            o[i][2] = o[i][2] * wa[1] + x.z * wb[1];
+            o[i][3] = o[i][3] * wa[1] + x.w * wb[1];
+        }
+    }
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
         if (row_pos[h2] < 0) continue;
-        const int row = warp * 16 + g + 8 * h2;
+        const int row = rg * 16 + g + 8 * h2;
         const int tl = row / hpc, h = row % hpc;
         const size_t n = (size_t)(q_begin + tok0 + tl);
         if (p.seg_keys > 0) {
@@ -327,16 +364,24 @@ LLMP_API int llmp_latent_attention_mma(const void* q_lat, long ql_t, long ql_h, 
     p.tokens_per_cta = LM_ROWS / p.hpc;
     p.head_chunks = (H + p.hpc - 1) / p.hpc;
     p.num_tiles = num_tiles;
-    p.v_chunks = (rank + LM_VCHUNK - 1) / LM_VCHUNK;
+    const int vchunk = rank > 128 ? 256 : 128;
+    p.v_chunks = (rank + vchunk - 1) / vchunk;
     p.seg_keys = seg_keys;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (size_t)segments * N * H * rank : nullptr;
     p.scale = scale;
     LLMP_REQUIRE((long)num_tiles * p.head_chunks < (1L << 31) && p.v_chunks <= 65535, "latent_attention_mma: too many tiles");
-    const size_t smem = sizeof(bf16) * (size_t)(LM_ROWS + LM_KEYS) * (rank + rot + 8);
-    LLMP_ALLOW_SMEM(latent_attention_mma_kernel, smem);
+    size_t smem = sizeof(bf16) * (size_t)(LM_ROWS + LM_KEYS) * (rank + rot + 8);
+    const size_t meet = sizeof(float) * 4 * 32 * (size_t)(vchunk / 2 + 4);       // where the halves of a row group meet
+    if (smem < meet) smem = meet;
     dim3 grid((unsigned)(num_tiles * p.head_chunks), p.v_chunks, seg_keys > 0 ? segments : 1);
-    latent_attention_mma_kernel<<<grid, LM_THREADS, smem, stream>>>(p);
+    if (vchunk == 128) {
+        LLMP_ALLOW_SMEM(latent_attention_mma_kernel<128>, smem);
+        latent_attention_mma_kernel<128><<<grid, LM_THREADS, smem, stream>>>(p);
+    } else {
+        LLMP_ALLOW_SMEM(latent_attention_mma_kernel<256>, smem);
+        latent_attention_mma_kernel<256><<<grid, LM_THREADS, smem, stream>>>(p);
+    }
     if (seg_keys > 0)
         latent_merge_kernel<<<dim3(N, H), 128, 0, stream>>>(p.part_o, p.part_ml, positions, (bf16*)out, o_t, o_h, N, H, rank, seg_keys);
     return llmp_check_launch("latent_attention_mma");

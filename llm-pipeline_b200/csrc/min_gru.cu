@@ -71,6 +71,7 @@ __global__ void min_gru_chunk_kernel(const GruArgs a) {
     const int t1 = min(end, t0 + SCAN_CHUNK);
     const float bz = a.bias[c], bx = a.bias[a.W + c];
     float A = 1.f, B = 0.f;
+#pragma unroll 8
     for (int t = t0; t < t1; ++t) {
         const float z = sigmoidf_(a.p[(size_t)t * 3 * a.W + c] + bz);
         const float u = a.p[(size_t)t * 3 * a.W + a.W + c] + bx;
@@ -118,6 +119,7 @@ __global__ void min_gru_apply_kernel(const GruArgs a) {
     const int t1 = min(end, t0 + SCAN_CHUNK);
     float s = a.chunk_a[((size_t)r * a.chunks + k) * a.W + c];
     const float bz = a.bias[c], bx = a.bias[a.W + c];
+#pragma unroll 8
     for (int t = t0; t < t1; ++t) {
         gru_step(a, t, c, bz, bx, s);
         gru_emit(a, t, c, s);

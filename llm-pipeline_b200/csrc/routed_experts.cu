@@ -12,14 +12,26 @@
 
 __global__ void route_topk_kernel(const void* __restrict__ h, int h_bf16, const float* __restrict__ wr, int top, int* __restrict__ ids,
                                   float* __restrict__ wts, int Hd, int E) {
-    extern __shared__ float logits[];                        // [E]
+    extern __shared__ float route_smem[];
+    float* logits = route_smem;                              // [E]
+    float* row = route_smem + E;                             // [Hd]: the token's row, read once
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < Hd; i += blockDim.x) row[i] = load_as_float(h, h_bf16, (size_t)n * Hd + i);
+    __syncthreads();
     for (int e = warp; e < E; e += nwarps) {
         const float* w = wr + (size_t)e * Hd;
-        float s = 0.f;
-        for (int i = lane; i < Hd; i += 32) s = fmaf(load_as_float(h, h_bf16, (size_t)n * Hd + i), w[i], s);
-        s = warp_sum(s);
+        // four sums a lane, so that four loads are in flight; their order of addition is fixed
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        int i = lane;
+        for (; i + 96 < Hd; i += 128) {
+            s0 = fmaf(row[i], w[i], s0);
+            s1 = fmaf(row[i + 32], w[i + 32], s1);
+            s2 = fmaf(row[i + 64], w[i + 64], s2);
+            s3 = fmaf(row[i + 96], w[i + 96], s3);
+        }
+        for (; i < Hd; i += 32) s0 = fmaf(row[i], w[i], s0);
+        const float s = warp_sum((s0 + s1) + (s2 + s3));
         if (lane == 0) logits[e] = s;
     }
     __syncthreads();
@@ -48,7 +60,10 @@ LLMP_API int llmp_route_topk(const void* h, int h_dtype, const float* w_router, 
                              cudaStream_t stream) {
     if (N <= 0) return 0;
     LLMP_REQUIRE(E > 0 && top > 0 && top <= E && Hd > 0 && E <= 8192, "route_topk: bad sizes experts=%d top=%d width=%d", E, top, Hd);
-    route_topk_kernel<<<N, 128, (size_t)E * sizeof(float), stream>>>(h, h_dtype == LLMP_BF16, w_router, top, ids, wts, Hd, E);
+    const size_t smem = (size_t)(E + Hd) * sizeof(float);
+    LLMP_REQUIRE(smem <= 200 * 1024, "route_topk: a row of %d entries does not fit shared memory", Hd);
+    LLMP_ALLOW_SMEM(route_topk_kernel, smem);
+    route_topk_kernel<<<N, 256, smem, stream>>>(h, h_dtype == LLMP_BF16, w_router, top, ids, wts, Hd, E);
     return llmp_check_launch("route_topk");
 }
 
@@ -115,4 +130,200 @@ LLMP_API int llmp_expert_rows(const void* h, const void* w_gu, const void* w_dow
         expert_down_kernel<bf16><<<g2, 256, 0, stream>>>((const bf16*)y, (const bf16*)w_down, ids, out, top, Hd, F);
     }
     return llmp_check_launch("expert_rows");
+}
+
+// ------------------------------------------------------------------------------------------
+// The grouped form for steps of many rows (bfloat16, tensor cores: mma.sync m16n8k16, float32 sums).
+//   count / plan / scatter: the (token, choice) pairs are sorted by expert on the device. Every expert's run of pairs
+//       starts at a multiple of 64 rows of the sorted order, so a tile of 64 rows has one expert; the places between an
+//       expert's last pair and the next multiple of 64 hold -1. Which place within its expert's run a pair gets
+//       depends on the order of atomic adds, but a row's result does not depend on its place.
+//   grouped products: a block takes a tile of 64 sorted rows and 64 output columns, its four warps 16 rows each.
+//       First product: rows gathered from h by pair, against the expert's gate rows and up rows of the same columns,
+//       with the activation in the epilogue (y, bfloat16, in sorted order). Second product: y against the expert's
+//       down rows, written as float32 at the pair's own place.
+//   combine: out[token] = sum of its pairs' rows in the order of its choices.
+// ------------------------------------------------------------------------------------------
+#define GX_ROWS 64
+#define GX_COLS 64
+#define GX_K 32
+#define GX_STRIDE (GX_K + 8)
+
+__global__ void moe_count_kernel(const int* __restrict__ ids, int pairs, int* __restrict__ counts) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < pairs) atomicAdd(&counts[ids[i]], 1);
+}
+
+// One block. counts[E] -> cursor[E] (first sorted row of each expert), the tile list and its length.
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ cursor, int* __restrict__ tile_expert,
+                                int* __restrict__ tile_row0, int* __restrict__ num_tiles) {
+    if (threadIdx.x != 0) return;
+    int row = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+        cursor[e] = row;
+        const int n = (counts[e] + GX_ROWS - 1) / GX_ROWS;
+        for (int k = 0; k < n; ++k) {
+            tile_expert[tiles] = e;
+            tile_row0[tiles] = row + k * GX_ROWS;
+            ++tiles;
+        }
+        row += n * GX_ROWS;
+    }
+    *num_tiles = tiles;
+}
+
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, int pairs, int* __restrict__ cursor, int* __restrict__ sorted_pair) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < pairs) sorted_pair[atomicAdd(&cursor[ids[i]], 1)] = i;
+}
+
+__device__ __forceinline__ void gx_cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void gx_ldmatrix_x4(unsigned (&r)[4], const void* smem_ptr) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+__device__ __forceinline__ void gx_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct GroupedArgs {
+    const bf16* a;            // first product: h [tokens, K]; second: y [sorted rows, K]
+    const bf16* w;            // first: [E, 2 cols_total, K]; second: [E, cols_total, K]
+    const int* sorted_pair; const int* tile_expert; const int* tile_row0; const int* num_tiles;
+    const float* wts;
+    bf16* y;                  // first product's result [sorted rows, cols_total]
+    float* out;               // second product's result [pairs, cols_total]
+    int top, K, cols_total;
+    float limit;
+};
+
+// GATED: the first product (two weight tiles, activation); else the second.
+template <bool GATED>
+__global__ void __launch_bounds__(128) moe_grouped_kernel(const GroupedArgs a) {
+    __shared__ __align__(16) bf16 As[GX_ROWS * GX_STRIDE];
+    __shared__ __align__(16) bf16 Bs[(GATED ? 2 : 1) * GX_COLS * GX_STRIDE];
+    __shared__ int row_pair[GX_ROWS];
+    const int tile = blockIdx.x;
+    if (tile >= *a.num_tiles) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int e = a.tile_expert[tile], row0 = a.tile_row0[tile];
+    const int col0 = blockIdx.y * GX_COLS;
+    if (tid < GX_ROWS) row_pair[tid] = a.sorted_pair[row0 + tid];
+    __syncthreads();
+    const bf16* wg = a.w + ((size_t)e * (GATED ? 2 : 1) * a.cols_total + col0) * a.K;
+    const bf16* wu = wg + (size_t)a.cols_total * a.K;
+    float cg[8][4], cu[GATED ? 8 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cg[i][0] = cg[i][1] = cg[i][2] = cg[i][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < (GATED ? 8 : 1); ++i) cu[i][0] = cu[i][1] = cu[i][2] = cu[i][3] = 0.f;
+    for (int k0 = 0; k0 < a.K; k0 += GX_K) {
+        for (int v = tid; v < GX_ROWS * (GX_K / 8); v += 128) {
+            const int row = v / (GX_K / 8), c = (v % (GX_K / 8)) * 8;
+            const int pair = row_pair[row];
+            const bool ok = pair >= 0 && k0 + c < a.K;
+            const size_t src_row = GATED ? (size_t)(pair / a.top) : (size_t)(row0 + row);
+            gx_cp_async_16(As + row * GX_STRIDE + c, ok ? a.a + src_row * a.K + k0 + c : a.a, ok);
+            const bool okw = col0 + row < a.cols_total && k0 + c < a.K;
+            gx_cp_async_16(Bs + row * GX_STRIDE + c, okw ? wg + (size_t)row * a.K + k0 + c : a.w, okw);
+            if (GATED) gx_cp_async_16(Bs + (GX_COLS + row) * GX_STRIDE + c, okw ? wu + (size_t)row * a.K + k0 + c : a.w, okw);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < GX_K / 16; ++ks) {
+            unsigned fa[4];
+            gx_ldmatrix_x4(fa, As + (warp * 16 + (lane & 15)) * GX_STRIDE + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < 8; nb += 2) {
+                unsigned fb[4];
+                gx_ldmatrix_x4(fb, Bs + ((nb + (lane >> 4)) * 8 + (lane & 7)) * GX_STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+                gx_mma(cg[nb], fa, fb[0], fb[1]);
+                gx_mma(cg[nb + 1], fa, fb[2], fb[3]);
+                if (GATED) {
+                    gx_ldmatrix_x4(fb, Bs + (GX_COLS + (nb + (lane >> 4)) * 8 + (lane & 7)) * GX_STRIDE + ks * 16 + ((lane >> 3) & 1) * 8);
+                    gx_mma(cu[nb], fa, fb[0], fb[1]);
+                    gx_mma(cu[nb + 1], fa, fb[2], fb[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        const int row = warp * 16 + g + 8 * h2;
+        const int pair = row_pair[row];
+        if (pair < 0) continue;
+        const float w = GATED ? a.wts[pair] : 0.f;
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+            for (int c2 = 0; c2 < 2; ++c2) {
+                const int col = col0 + nb * 8 + 2 * t + c2;
+                if (col >= a.cols_total) continue;
+                if (GATED) a.y[(size_t)(row0 + row) * a.cols_total + col] = __float2bfloat16_rn(expert_act(cg[nb][2 * h2 + c2], cu[GATED ? nb : 0][2 * h2 + c2], w, a.limit));
+                else a.out[(size_t)pair * a.cols_total + col] = cg[nb][2 * h2 + c2];
+            }
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ pair_out, float* __restrict__ out, int top, int Hd, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t n = i / Hd, c = i % Hd;
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) s += pair_out[(n * top + k) * Hd + c];
+    out[i] = s;
+}
+
+LLMP_API int llmp_expert_grouped_supports(int Hd, int F) { return Hd % 8 == 0 && F % 8 == 0; }
+
+// Rows of the sorted order for `pairs` pairs among E experts (every expert's run padded to a multiple of 64).
+LLMP_API long llmp_expert_grouped_rows(int pairs, int E) { return ((long)(pairs + GX_ROWS - 1) / GX_ROWS + E) * GX_ROWS; }
+
+// ints: int32 scratch [3 E + 1 + 2 tiles_max + rows_max] with tiles_max = rows_max / 64; y: bf16 [rows_max, F];
+// pair_out: float32 [pairs, Hd] (unused when top == 1: the rows go straight to out).
+LLMP_API int llmp_expert_grouped(const void* h, const void* w_gu, const void* w_down, const int* ids, const float* wts, float limit,
+                                 int* ints, void* y, float* pair_out, float* out, int N, int top, int Hd, int F, int E,
+                                 cudaStream_t stream) {
+    if (N <= 0) return 0;
+    LLMP_REQUIRE(llmp_expert_grouped_supports(Hd, F) && top > 0 && E > 0, "expert_grouped: sizes width=%d ff=%d are not served", Hd, F);
+    const int pairs = N * top;
+    const long rows_max = llmp_expert_grouped_rows(pairs, E);
+    const int tiles_max = (int)(rows_max / GX_ROWS);
+    int* counts = ints;
+    int* cursor = ints + E;
+    int* num_tiles = ints + 2 * E;
+    int* tile_expert = ints + 2 * E + 1;
+    int* tile_row0 = tile_expert + tiles_max;
+    int* sorted_pair = tile_row0 + tiles_max;
+    cudaMemsetAsync(counts, 0, sizeof(int) * E, stream);
+    cudaMemsetAsync(sorted_pair, 0xFF, sizeof(int) * rows_max, stream);
+    moe_count_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, counts);
+    moe_plan_kernel<<<1, 32, 0, stream>>>(counts, E, cursor, tile_expert, tile_row0, num_tiles);
+    moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, cursor, sorted_pair);
+    GroupedArgs a;
+    a.sorted_pair = sorted_pair; a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.num_tiles = num_tiles;
+    a.wts = wts; a.y = (bf16*)y; a.top = top; a.limit = limit;
+    a.a = (const bf16*)h; a.w = (const bf16*)w_gu; a.K = Hd; a.cols_total = F; a.out = nullptr;
+    moe_grouped_kernel<true><<<dim3(tiles_max, (F + GX_COLS - 1) / GX_COLS), 128, 0, stream>>>(a);
+    a.a = (const bf16*)y; a.w = (const bf16*)w_down; a.K = F; a.cols_total = Hd; a.out = top == 1 ? out : pair_out;
+    moe_grouped_kernel<false><<<dim3(tiles_max, (Hd + GX_COLS - 1) / GX_COLS), 128, 0, stream>>>(a);
+    if (top > 1) {
+        const size_t total = (size_t)N * Hd;
+        moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(pair_out, out, top, Hd, total);
+    }
+    return llmp_check_launch("expert_grouped");
 }

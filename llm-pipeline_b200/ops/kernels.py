@@ -68,6 +68,7 @@ _SIGNATURES = {
     "llmp_latent_attention_mma": [_P, _L, _L, _P, _L, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I, _F, _I,
                                   _I, _P, _P],
     "llmp_route_topk": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _P],
+    "llmp_expert_grouped": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "llmp_expert_rows": [_P, _P, _P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P],
 }
 _bound = {}
@@ -910,9 +911,48 @@ def expert_rows(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     return out
 
 
+EXPERT_GROUPED_MIN_ROWS = 33         # (token, choice) pairs from which a step's experts run as grouped products
+
+
+def expert_grouped_supports(dtype: torch.dtype, Hd: int, F: int) -> bool:
+    if dtype != torch.bfloat16:
+        return False
+    fn = library().llmp_expert_grouped_supports
+    fn.argtypes = [_I, _I]
+    fn.restype = _I
+    return bool(fn(Hd, F))
+
+
+def expert_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                   limit: float, out: torch.Tensor) -> torch.Tensor:
+    """``expert_rows`` for many rows (bfloat16): the pairs are sorted by expert on the device and the experts' products
+    run as grouped tensor-core products that read an expert's rows once per 64 pairs."""
+    N, Hd = h.shape
+    E, two_f, _ = w_gate_up.shape
+    F = two_f // 2
+    top = ids.shape[1]
+    _need(h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_gate_up.shape == (E, 2 * F, Hd) and
+          w_down.shape == (E, Hd, F) and h.dtype == w_gate_up.dtype == w_down.dtype == torch.bfloat16, "expert matrices have the wrong layout")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (N, Hd), "expert output must be float32 [tokens, width]")
+    fn = library().llmp_expert_grouped_rows
+    fn.argtypes = [_I, _I]
+    fn.restype = _L
+    rows = int(fn(N * top, E))
+    ints = torch.empty(3 * E + 1 + 2 * (rows // 64) + rows, dtype=torch.int32, device=h.device)
+    y = torch.empty((rows, F), dtype=torch.bfloat16, device=h.device)
+    pair_out = torch.empty((N * top, Hd), dtype=torch.float32, device=h.device) if top > 1 else None
+    _call("llmp_expert_grouped", _ptr(h), _ptr(w_gate_up), _ptr(w_down), _ptr(ids), _ptr(weights), float(limit), _ptr(ints), _ptr(y),
+          _ptr(pair_out), _ptr(out), N, top, Hd, F, E, _stream())
+    return out
+
+
 def routed_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                    limit: float, out: torch.Tensor) -> torch.Tensor:
-    """The experts' work for a step's rows, by the kernel that suits their number (``expert_rows`` for few)."""
+    """The experts' work for a step's rows, by the kernel that suits their number: grouped tensor-core products for many
+    bfloat16 rows, a warp per output entry (``expert_rows``) for the few rows of a decode step and for float32."""
+    pairs = ids.numel()
+    if pairs >= EXPERT_GROUPED_MIN_ROWS and expert_grouped_supports(h.dtype, h.shape[1], w_down.shape[2]):
+        return expert_grouped(h, w_gate_up, w_down, ids, weights, limit, out)
     return expert_rows(h, w_gate_up, w_down, ids, weights, limit, out)
 
 
