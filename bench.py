@@ -651,7 +651,7 @@ def zupilorn_work(z, tokens, keys_per_token, decode):
         work["expert_rows"] = (att_layers * pairs * expert_weights, 0.0)
     else:
         work["expert_rows"] = (0.0, att_layers * 2.0 * pairs * 3 * z["expert_ff"] * D)
-    work["routed_experts_grouped"] = work["expert_rows"]
+    work["expert_grouped"] = work["expert_rows"]
     return work
 
 

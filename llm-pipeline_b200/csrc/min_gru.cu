@@ -15,7 +15,8 @@
 
 #define SCAN_CHUNK 64
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+// 1 / (1 + e^-x) with a correctly rounded reciprocal (one special-function instruction and a fix-up, not a division)
+__device__ __forceinline__ float sigmoidf_(float x) { return __frcp_rn(1.f + expf(-x)); }
 
 struct GruArgs {
     const float* p;          // [N, 3 W]
@@ -25,25 +26,27 @@ struct GruArgs {
     const int* positions;    // [N]
     float* state;            // [slots, 2, W]
     void* out; int out_bf16; // [N, W]
-    float* chunk_a; float* chunk_b;   // [R, chunks, W] (chunked path)
+    float* chunk_a; float* chunk_b;   // [R, chunks, W] (chunked path): A and B of every chunk
+    float* chunk_s;                   // [R, chunks, W]: the state before every chunk
     int W, chunks;
 };
 
-__device__ __forceinline__ void gru_step(const GruArgs& a, size_t row, int c, float bz, float bx, float& s) {
-    const float z = sigmoidf_(a.p[row * 3 * a.W + c] + bz);
-    const float u = a.p[row * 3 * a.W + a.W + c] + bx;
+// One token of one channel. The pointers are local and restricted, so that the loads of the next tokens need not wait
+// for this token's store: an unrolled loop keeps several rows of the products in flight.
+template <typename TO>
+__device__ __forceinline__ void gru_token(const float* __restrict__ p, TO* __restrict__ out, size_t row, int W, int c, float bz,
+                                          float bx, float& s) {
+    const float* pr = p + row * 3 * W;
+    const float z = sigmoidf_(pr[c] + bz);
+    const float u = pr[W + c] + bx;
+    const float g = pr[2 * W + c];
     const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
     s = (1.f - z) * s + z * cand;
-}
-
-__device__ __forceinline__ void gru_emit(const GruArgs& a, size_t row, int c, float s) {
-    const float g = a.p[row * 3 * a.W + 2 * a.W + c];
-    const float y = s * (g * sigmoidf_(g));
-    if (a.out_bf16) reinterpret_cast<bf16*>(a.out)[row * a.W + c] = __float2bfloat16_rn(y);
-    else reinterpret_cast<float*>(a.out)[row * a.W + c] = y;
+    out[row * W + c] = from_float<TO>(s * (g * sigmoidf_(g)));
 }
 
 // One thread per (request, channel): walks the request's tokens of this step in order.
+template <typename TO>
 __global__ void min_gru_serial_kernel(const GruArgs a) {
     const int r = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -54,10 +57,10 @@ __global__ void min_gru_serial_kernel(const GruArgs a) {
     float* st = a.state + (size_t)a.slots[r] * 2 * a.W;
     float s = st[((p0 + 1) & 1) * a.W + c];
     const float bz = a.bias[c], bx = a.bias[a.W + c];
-    for (int t = t0; t < t1; ++t) {
-        gru_step(a, t, c, bz, bx, s);
-        gru_emit(a, t, c, s);
-    }
+    const float* __restrict__ p = a.p;
+    TO* __restrict__ out = reinterpret_cast<TO*>(a.out);
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) gru_token<TO>(p, out, t, a.W, c, bz, bx, s);
     st[((p0 + t1 - t0 - 1) & 1) * a.W + c] = s;
 }
 
@@ -71,10 +74,11 @@ __global__ void min_gru_chunk_kernel(const GruArgs a) {
     const int t1 = min(end, t0 + SCAN_CHUNK);
     const float bz = a.bias[c], bx = a.bias[a.W + c];
     float A = 1.f, B = 0.f;
+    const float* __restrict__ p = a.p;
 #pragma unroll 8
     for (int t = t0; t < t1; ++t) {
-        const float z = sigmoidf_(a.p[(size_t)t * 3 * a.W + c] + bz);
-        const float u = a.p[(size_t)t * 3 * a.W + a.W + c] + bx;
+        const float z = sigmoidf_(p[(size_t)t * 3 * a.W + c] + bz);
+        const float u = p[(size_t)t * 3 * a.W + a.W + c] + bx;
         const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
         A *= 1.f - z;
         B = (1.f - z) * B + z * cand;
@@ -84,8 +88,8 @@ __global__ void min_gru_chunk_kernel(const GruArgs a) {
     a.chunk_b[at] = B;
 }
 
-// Chunked path, second kernel: one thread per (request, channel) walks the request's chunks in order, replaces every
-// chunk's A by the state before that chunk, and leaves the request's new state. It is the only kernel of the chunked
+// Chunked path, second kernel: one thread per (request, channel) walks the request's chunks in order, leaves the state
+// before every chunk, and leaves the request's new state. It is the only kernel of the chunked
 // path that touches the state, and it reads before it writes, so an even number of tokens (same vector read and
 // written) is no hazard.
 __global__ void min_gru_prefix_kernel(const GruArgs a) {
@@ -99,16 +103,20 @@ __global__ void min_gru_prefix_kernel(const GruArgs a) {
     float* st = a.state + (size_t)a.slots[r] * 2 * a.W;
     float s = st[((p0 + 1) & 1) * a.W + c];
     const int chunks = (n + SCAN_CHUNK - 1) / SCAN_CHUNK;
+    const float* __restrict__ As = a.chunk_a;
+    const float* __restrict__ Bs = a.chunk_b;
+    float* __restrict__ Ss = a.chunk_s;
+#pragma unroll 8
     for (int k = 0; k < chunks; ++k) {
         const size_t at = ((size_t)r * a.chunks + k) * a.W + c;
-        const float A = a.chunk_a[at], B = a.chunk_b[at];
-        a.chunk_a[at] = s;
-        s = A * s + B;
+        Ss[at] = s;
+        s = As[at] * s + Bs[at];
     }
     st[((p0 + n - 1) & 1) * a.W + c] = s;
 }
 
 // Chunked path, third kernel: the chunk's tokens from the state before the chunk.
+template <typename TO>
 __global__ void min_gru_apply_kernel(const GruArgs a) {
     const int r = blockIdx.x, k = blockIdx.y;
     const int c = blockIdx.z * blockDim.x + threadIdx.x;
@@ -117,18 +125,17 @@ __global__ void min_gru_apply_kernel(const GruArgs a) {
     const int t0 = a.q_start[r] + k * SCAN_CHUNK;
     if (t0 >= end) return;
     const int t1 = min(end, t0 + SCAN_CHUNK);
-    float s = a.chunk_a[((size_t)r * a.chunks + k) * a.W + c];
+    float s = a.chunk_s[((size_t)r * a.chunks + k) * a.W + c];
     const float bz = a.bias[c], bx = a.bias[a.W + c];
+    const float* __restrict__ p = a.p;
+    TO* __restrict__ out = reinterpret_cast<TO*>(a.out);
 #pragma unroll 8
-    for (int t = t0; t < t1; ++t) {
-        gru_step(a, t, c, bz, bx, s);
-        gru_emit(a, t, c, s);
-    }
+    for (int t = t0; t < t1; ++t) gru_token<TO>(p, out, t, a.W, c, bz, bx, s);
 }
 
 LLMP_API int llmp_min_gru_chunk() { return SCAN_CHUNK; }
 
-// scratch: float32 [2, R, chunks, W] when max_q_len > SCAN_CHUNK (chunks = ceil(max_q_len / SCAN_CHUNK)), else unused.
+// scratch: float32 [3, R, chunks, W] when max_q_len > SCAN_CHUNK (chunks = ceil(max_q_len / SCAN_CHUNK)), else unused.
 LLMP_API int llmp_min_gru(const float* p, const float* bias, const int* q_start, const int* slots, const int* positions,
                           float* state, void* out, int out_dtype, float* scratch, int R, int W, int max_q_len,
                           cudaStream_t stream) {
@@ -137,11 +144,12 @@ LLMP_API int llmp_min_gru(const float* p, const float* bias, const int* q_start,
     GruArgs a;
     a.p = p; a.bias = bias; a.q_start = q_start; a.slots = slots; a.positions = positions; a.state = state;
     a.out = out; a.out_bf16 = out_dtype == LLMP_BF16; a.W = W;
-    a.chunk_a = a.chunk_b = nullptr; a.chunks = 0;
+    a.chunk_a = a.chunk_b = a.chunk_s = nullptr; a.chunks = 0;
     const int threads = 128;
     const int col_blocks = (W + threads - 1) / threads;
     if (max_q_len <= SCAN_CHUNK) {
-        min_gru_serial_kernel<<<dim3(R, col_blocks), threads, 0, stream>>>(a);
+        if (a.out_bf16) min_gru_serial_kernel<bf16><<<dim3(R, col_blocks), threads, 0, stream>>>(a);
+        else min_gru_serial_kernel<float><<<dim3(R, col_blocks), threads, 0, stream>>>(a);
         return llmp_check_launch("min_gru");
     }
     LLMP_REQUIRE(scratch != nullptr, "min_gru: portions of more than %d tokens need scratch", SCAN_CHUNK);
@@ -149,8 +157,10 @@ LLMP_API int llmp_min_gru(const float* p, const float* bias, const int* q_start,
     LLMP_REQUIRE(a.chunks <= 65535 && col_blocks <= 65535, "min_gru: too many chunks %d", a.chunks);
     a.chunk_a = scratch;
     a.chunk_b = scratch + (size_t)R * a.chunks * W;
+    a.chunk_s = scratch + 2 * (size_t)R * a.chunks * W;
     min_gru_chunk_kernel<<<dim3(R, a.chunks, col_blocks), threads, 0, stream>>>(a);
     min_gru_prefix_kernel<<<dim3(R, col_blocks), threads, 0, stream>>>(a);
-    min_gru_apply_kernel<<<dim3(R, a.chunks, col_blocks), threads, 0, stream>>>(a);
+    if (a.out_bf16) min_gru_apply_kernel<bf16><<<dim3(R, a.chunks, col_blocks), threads, 0, stream>>>(a);
+    else min_gru_apply_kernel<float><<<dim3(R, a.chunks, col_blocks), threads, 0, stream>>>(a);
     return llmp_check_launch("min_gru (chunked)");
 }

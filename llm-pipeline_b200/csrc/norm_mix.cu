@@ -129,7 +129,9 @@ LLMP_API int llmp_add_norm_mix(float* residual, const void* delta, int delta_dty
     a.rows = rows; a.H = H;
     const size_t smem = (size_t)H * sizeof(float);
     LLMP_ALLOW_SMEM(add_norm_mix_kernel, smem);
-    add_norm_mix_kernel<<<M, H >= 2048 ? 512 : 128, smem, stream>>>(a);
+    // few rows (a decode step): as many threads as the row has pairs of entries, so that a thread's loads are few
+    const int threads = (M <= 256 && H >= 512) ? (H >= 2048 ? 1024 : (H / 2 + 31) / 32 * 32) : (H >= 2048 ? 512 : 128);
+    add_norm_mix_kernel<<<M, threads, smem, stream>>>(a);
     return llmp_check_launch("add_norm_mix");
 }
 

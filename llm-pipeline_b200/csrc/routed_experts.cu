@@ -21,17 +21,17 @@ __global__ void route_topk_kernel(const void* __restrict__ h, int h_bf16, const 
     __syncthreads();
     for (int e = warp; e < E; e += nwarps) {
         const float* w = wr + (size_t)e * Hd;
-        // four sums a lane, so that four loads are in flight; their order of addition is fixed
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        // eight sums a lane, so that eight loads are in flight; their order of addition is fixed
+        float acc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[u] = 0.f;
         int i = lane;
-        for (; i + 96 < Hd; i += 128) {
-            s0 = fmaf(row[i], w[i], s0);
-            s1 = fmaf(row[i + 32], w[i + 32], s1);
-            s2 = fmaf(row[i + 64], w[i + 64], s2);
-            s3 = fmaf(row[i + 96], w[i + 96], s3);
+        for (; i + 7 * 32 < Hd; i += 256) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[u] = fmaf(row[i + 32 * u], w[i + 32 * u], acc[u]);
         }
-        for (; i < Hd; i += 32) s0 = fmaf(row[i], w[i], s0);
-        const float s = warp_sum((s0 + s1) + (s2 + s3));
+        for (; i < Hd; i += 32) acc[0] = fmaf(row[i], w[i], acc[0]);
+        const float s = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7])));
         if (lane == 0) logits[e] = s;
     }
     __syncthreads();
@@ -63,7 +63,8 @@ LLMP_API int llmp_route_topk(const void* h, int h_dtype, const float* w_router, 
     const size_t smem = (size_t)(E + Hd) * sizeof(float);
     LLMP_REQUIRE(smem <= 200 * 1024, "route_topk: a row of %d entries does not fit shared memory", Hd);
     LLMP_ALLOW_SMEM(route_topk_kernel, smem);
-    route_topk_kernel<<<N, 256, smem, stream>>>(h, h_dtype == LLMP_BF16, w_router, top, ids, wts, Hd, E);
+    // few rows (a decode step): a warp per expert, so that the router matrix is read by many warps at once
+    route_topk_kernel<<<N, N <= 64 ? 1024 : 256, smem, stream>>>(h, h_dtype == LLMP_BF16, w_router, top, ids, wts, Hd, E);
     return llmp_check_launch("route_topk");
 }
 

@@ -837,7 +837,7 @@ def min_gru(p: torch.Tensor, bias: torch.Tensor, q_start: torch.Tensor, slots: t
     scratch = None
     chunk = min_gru_chunk()
     if max_q_len > chunk:
-        scratch = torch.empty((2, R, -(-max_q_len // chunk), W), dtype=torch.float32, device=p.device)
+        scratch = torch.empty((3, R, -(-max_q_len // chunk), W), dtype=torch.float32, device=p.device)
     _call("llmp_min_gru", _ptr(p), _ptr(bias), _ptr(q_start), _ptr(slots), _ptr(positions), _ptr(state), _ptr(out),
           dtype_code(out.dtype), _ptr(scratch), R, W, int(max_q_len), _stream())
     return out
