@@ -140,25 +140,30 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
     const bool warp_has_rows = warp_first_tok < ntok;
     const int warp_lo_pos = pos0 + tok0 + (warp_first_tok < ntok ? warp_first_tok : ntok - 1);
     const bf16* Qw = Qs + (size_t)(rg * 16 + (lane & 15)) * STRIDE + (lane >> 4) * 8;
+    // The four warps of a key half are a pipeline of their own: they copy and read only their 32 rows of the key tile and
+    // meet at a barrier of their own, so one half's copies run under the other half's products.
+    const int gtid = tid & 127;                                   // thread within the half's four warps
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();                                              // the query tile is in place for everybody
     for (int j0 = (lo / LM_KEYS) * LM_KEYS; j0 <= hi; j0 += LM_KEYS) {
-        if (tid < LM_KEYS) {
-            const int j = j0 + tid;
+        if (gtid < 32) {
+            const int j = j0 + half * 32 + gtid;
             long long off = -1;
             if (j <= hi) {
                 const int page = table[j / p.page_size];
                 if (page >= 0) off = (long long)((size_t)page * p.page_size + (j % p.page_size)) * dk;
             }
-            key_off[tid] = off;
+            key_off[half * 32 + gtid] = off;
         }
-        __syncthreads();
-        for (int e = tid; e < LM_KEYS * vec_per_row; e += LM_THREADS) {
-            const int key = e / vec_per_row, c = (e % vec_per_row) * 8;
+        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+        for (int e = gtid; e < 32 * vec_per_row; e += 128) {
+            const int key = half * 32 + e / vec_per_row, c = (e % vec_per_row) * 8;
             const long long off = key_off[key];
             lm_cp_async_16(Ks + (size_t)key * STRIDE + c, off >= 0 ? p.pages + off + c : p.pages, off >= 0);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        __syncthreads();
+        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
         do {
             const int jh = j0 + half * 32;
             if (!warp_has_rows || jh > warp_hi_pos || jh > hi) break;      // no row of this warp sees these keys
@@ -241,7 +246,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
                 }
             }
         } while (false);
-        __syncthreads();                                         // the tile's buffer may be overwritten now
+        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");      // the half's rows may be overwritten now
     }
 
 #pragma unroll
@@ -255,6 +260,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
         float* xo = reinterpret_cast<float*>(lm_smem);            // [4 row groups][32 lanes][LM_VCHUNK / 2 + 4]
         constexpr int PER_LANE = LM_VCHUNK / 2 + 4;
         float* mine = xo + ((size_t)rg * 32 + lane) * PER_LANE;
+        __syncthreads();                                          // both halves are done with the query and key tiles
         if (half == 1) {
 #pragma unroll
             for (int i = 0; i < LM_VCHUNK / 8; ++i)

@@ -147,7 +147,7 @@ LLMP_API int llmp_expert_rows(const void* h, const void* w_gu, const void* w_dow
 // ------------------------------------------------------------------------------------------
 #define GX_ROWS 64
 #define GX_COLS 64
-#define GX_K 32
+#define GX_K 64
 #define GX_STRIDE (GX_K + 8)
 
 __global__ void moe_count_kernel(const int* __restrict__ ids, int pairs, int* __restrict__ counts) {
@@ -210,8 +210,12 @@ struct GroupedArgs {
 // GATED: the first product (two weight tiles, activation); else the second.
 template <bool GATED>
 __global__ void __launch_bounds__(128) moe_grouped_kernel(const GroupedArgs a) {
-    __shared__ __align__(16) bf16 As[GX_ROWS * GX_STRIDE];
-    __shared__ __align__(16) bf16 Bs[(GATED ? 2 : 1) * GX_COLS * GX_STRIDE];
+    // two stages of [A tile | weight tile(s)], each tile [64][GX_STRIDE]: the copies of the next K step run under the
+    // products of this one
+    extern __shared__ __align__(16) unsigned char gx_smem[];
+    constexpr int TILES = GATED ? 3 : 2;
+    constexpr int STAGE = TILES * GX_ROWS * GX_STRIDE;
+    bf16* ring = reinterpret_cast<bf16*>(gx_smem);
     __shared__ int row_pair[GX_ROWS];
     const int tile = blockIdx.x;
     if (tile >= *a.num_tiles) return;
@@ -228,7 +232,10 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const GroupedArgs a) {
     for (int i = 0; i < 8; ++i) cg[i][0] = cg[i][1] = cg[i][2] = cg[i][3] = 0.f;
 #pragma unroll
     for (int i = 0; i < (GATED ? 8 : 1); ++i) cu[i][0] = cu[i][1] = cu[i][2] = cu[i][3] = 0.f;
-    for (int k0 = 0; k0 < a.K; k0 += GX_K) {
+
+    auto copy_step = [&](int k0, int stage) {
+        bf16* As = ring + (size_t)stage * STAGE;
+        bf16* Bs = As + GX_ROWS * GX_STRIDE;
         for (int v = tid; v < GX_ROWS * (GX_K / 8); v += 128) {
             const int row = v / (GX_K / 8), c = (v % (GX_K / 8)) * 8;
             const int pair = row_pair[row];
@@ -240,8 +247,20 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const GroupedArgs a) {
             if (GATED) gx_cp_async_16(Bs + (GX_COLS + row) * GX_STRIDE + c, okw ? wu + (size_t)row * a.K + k0 + c : a.w, okw);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    };
+
+    copy_step(0, 0);
+    int stage = 0;
+    for (int k0 = 0; k0 < a.K; k0 += GX_K, stage ^= 1) {
+        if (k0 + GX_K < a.K) {
+            copy_step(k0 + GX_K, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
         __syncthreads();
+        const bf16* As = ring + (size_t)stage * STAGE;
+        const bf16* Bs = As + GX_ROWS * GX_STRIDE;
 #pragma unroll
         for (int ks = 0; ks < GX_K / 16; ++ks) {
             unsigned fa[4];
@@ -259,7 +278,7 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const GroupedArgs a) {
                 }
             }
         }
-        __syncthreads();
+        __syncthreads();                                         // the stage may be overwritten by the copies after next
     }
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
@@ -319,9 +338,12 @@ LLMP_API int llmp_expert_grouped(const void* h, const void* w_gu, const void* w_
     a.sorted_pair = sorted_pair; a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.num_tiles = num_tiles;
     a.wts = wts; a.y = (bf16*)y; a.top = top; a.limit = limit;
     a.a = (const bf16*)h; a.w = (const bf16*)w_gu; a.K = Hd; a.cols_total = F; a.out = nullptr;
-    moe_grouped_kernel<true><<<dim3(tiles_max, (F + GX_COLS - 1) / GX_COLS), 128, 0, stream>>>(a);
+    const size_t smem_gated = sizeof(bf16) * 2 * 3 * GX_ROWS * GX_STRIDE, smem_plain = sizeof(bf16) * 2 * 2 * GX_ROWS * GX_STRIDE;
+    LLMP_ALLOW_SMEM(moe_grouped_kernel<true>, smem_gated);
+    moe_grouped_kernel<true><<<dim3(tiles_max, (F + GX_COLS - 1) / GX_COLS), 128, smem_gated, stream>>>(a);
     a.a = (const bf16*)y; a.w = (const bf16*)w_down; a.K = F; a.cols_total = Hd; a.out = top == 1 ? out : pair_out;
-    moe_grouped_kernel<false><<<dim3(tiles_max, (Hd + GX_COLS - 1) / GX_COLS), 128, 0, stream>>>(a);
+    LLMP_ALLOW_SMEM(moe_grouped_kernel<false>, smem_plain);
+    moe_grouped_kernel<false><<<dim3(tiles_max, (Hd + GX_COLS - 1) / GX_COLS), 128, smem_plain, stream>>>(a);
     if (top > 1) {
         const size_t total = (size_t)N * Hd;
         moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(pair_out, out, top, Hd, total);
