@@ -96,7 +96,22 @@ LLMP_API int llmp_gemm_simt(const void* A, const void* W, const void* bias, int 
 // row once and keeps one sum per row of A; the K products of a sum are added lane by lane in ascending k, then across
 // the lanes in a fixed order.
 #define GR_MAX_ROWS 16
-template <typename TI, typename TO>
+__device__ __forceinline__ void gr_load8(const bf16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __low2float(h2[i]);
+        v[2 * i + 1] = __high2float(h2[i]);
+    }
+}
+__device__ __forceinline__ void gr_load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// VEC: K, the strides and the addresses allow 16-byte loads of 8 consecutive entries.
+template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
 gemm_rows_kernel(const TI* __restrict__ A, const TI* __restrict__ W, TO* __restrict__ C, int M, int N, int K, long lda, long ldw,
                  long ldc, long batch_a, long batch_w, long batch_c) {
@@ -109,11 +124,27 @@ gemm_rows_kernel(const TI* __restrict__ A, const TI* __restrict__ W, TO* __restr
     float acc[GR_MAX_ROWS];
 #pragma unroll
     for (int m = 0; m < GR_MAX_ROWS; ++m) acc[m] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-        const float wv = to_float(w[k]);
+    if (VEC) {
+        for (int k = lane * 8; k < K; k += 256) {
+            float wv[8];
+            gr_load8(w + k, wv);
 #pragma unroll
-        for (int m = 0; m < GR_MAX_ROWS; ++m)
-            if (m < M) acc[m] = fmaf(to_float(A[(size_t)m * lda + k]), wv, acc[m]);
+            for (int m = 0; m < GR_MAX_ROWS; ++m) {
+                if (m < M) {
+                    float xv[8];
+                    gr_load8(A + (size_t)m * lda + k, xv);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[m] = fmaf(xv[j], wv[j], acc[m]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_float(w[k]);
+#pragma unroll
+            for (int m = 0; m < GR_MAX_ROWS; ++m)
+                if (m < M) acc[m] = fmaf(to_float(A[(size_t)m * lda + k]), wv, acc[m]);
+        }
     }
 #pragma unroll
     for (int m = 0; m < GR_MAX_ROWS; ++m) {
@@ -135,19 +166,24 @@ LLMP_API int llmp_gemm_simt_batched(const void* A, const void* W, void* C, int i
     LLMP_REQUIRE((M + GT_BM - 1) / GT_BM <= 65535 && batch <= 65535, "batched gemm: too many rows %d or products %d", M, batch);
     if (M <= GR_MAX_ROWS && (N + 7) / 8 <= 65535) {
         dim3 rows_grid((N + 7) / 8, batch);
-        if (in_dtype == LLMP_F32 && out_dtype == LLMP_F32)
-            gemm_rows_kernel<float, float><<<rows_grid, 256, 0, stream>>>((const float*)A, (const float*)W, (float*)C, M, N, K, lda, ldw,
-                                                                          ldc, batch_a, batch_w, batch_c);
-        else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_BF16)
-            gemm_rows_kernel<bf16, bf16><<<rows_grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc,
-                                                                        batch_a, batch_w, batch_c);
-        else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_F32)
-            gemm_rows_kernel<bf16, float><<<rows_grid, 256, 0, stream>>>((const bf16*)A, (const bf16*)W, (float*)C, M, N, K, lda, ldw, ldc,
-                                                                         batch_a, batch_w, batch_c);
+        const size_t esize = in_dtype == LLMP_F32 ? 4 : 2;
+        const bool vec = K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && batch_a % 8 == 0 && batch_w % 8 == 0 &&
+                         ((size_t)A | (size_t)W) % 16 == 0 && esize > 0;
+#define LLMP_ROWS(TI, TO)                                                                                                         \
+    do {                                                                                                                          \
+        if (vec) gemm_rows_kernel<TI, TO, true><<<rows_grid, 256, 0, stream>>>((const TI*)A, (const TI*)W, (TO*)C, M, N, K, lda, ldw,   \
+                                                                               ldc, batch_a, batch_w, batch_c);                  \
+        else gemm_rows_kernel<TI, TO, false><<<rows_grid, 256, 0, stream>>>((const TI*)A, (const TI*)W, (TO*)C, M, N, K, lda, ldw, ldc, \
+                                                                            batch_a, batch_w, batch_c);                          \
+    } while (0)
+        if (in_dtype == LLMP_F32 && out_dtype == LLMP_F32) LLMP_ROWS(float, float);
+        else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_BF16) LLMP_ROWS(bf16, bf16);
+        else if (in_dtype == LLMP_BF16 && out_dtype == LLMP_F32) LLMP_ROWS(bf16, float);
         else {
             llmp_set_error("batched gemm: unsupported type combination in=%d out=%d", in_dtype, out_dtype);
             return 1;
         }
+#undef LLMP_ROWS
         return llmp_check_launch("gemm_simt_batched (rows)");
     }
     dim3 grid((N + GT_BN - 1) / GT_BN, (M + GT_BM - 1) / GT_BM, batch);

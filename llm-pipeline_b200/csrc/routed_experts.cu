@@ -74,8 +74,25 @@ __device__ __forceinline__ float expert_act(float g, float u, float w, float lim
     return g * (1.f / (1.f + expf(-1.702f * g))) * (u + 1.f);
 }
 
+// Eight consecutive entries of a row as floats, by 16-byte loads (the rows are 16-byte aligned when their length is a
+// multiple of 8 and the tensors are).
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __low2float(h2[i]);
+        v[2 * i + 1] = __high2float(h2[i]);
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
 // grid (pairs, ceil(F / 8)): a warp per row of the expert's gate and up matrices (w_gu[e] = [gate rows; up rows]).
-template <typename T>
+// VEC: the rows' length is a multiple of 8; a lane then takes 8 consecutive entries a step, in 16-byte loads.
+template <typename T, bool VEC>
 __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ ids,
                                       const float* __restrict__ wts, float limit, T* __restrict__ y, int top, int Hd, int F) {
     const int pair = blockIdx.x;
@@ -87,10 +104,25 @@ __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restri
     const T* wg = w_gu + ((size_t)e * 2 * F + f) * Hd;
     const T* wu = wg + (size_t)F * Hd;
     float g = 0.f, u = 0.f;
-    for (int i = lane; i < Hd; i += 32) {
-        const float xv = to_float(x[i]);
-        g = fmaf(xv, to_float(wg[i]), g);
-        u = fmaf(xv, to_float(wu[i]), u);
+    if (VEC) {
+#pragma unroll 2
+        for (int i = lane * 8; i < Hd; i += 256) {
+            float xv[8], a[8], b[8];
+            load8(x + i, xv);
+            load8(wg + i, a);
+            load8(wu + i, b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                g = fmaf(xv[j], a[j], g);
+                u = fmaf(xv[j], b[j], u);
+            }
+        }
+    } else {
+        for (int i = lane; i < Hd; i += 32) {
+            const float xv = to_float(x[i]);
+            g = fmaf(xv, to_float(wg[i]), g);
+            u = fmaf(xv, to_float(wu[i]), u);
+        }
     }
     g = warp_sum(g);
     u = warp_sum(u);
@@ -98,7 +130,7 @@ __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restri
 }
 
 // grid (tokens, ceil(Hd / 8)): a warp per output entry, the token's choices added in their order.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict__ w_down, const int* __restrict__ ids,
                                    float* __restrict__ out, int top, int Hd, int F) {
     const int n = blockIdx.x;
@@ -111,7 +143,18 @@ __global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict_
         const T* w = w_down + ((size_t)ids[pair] * Hd + c) * F;
         const T* yv = y + (size_t)pair * F;
         float s = 0.f;
-        for (int i = lane; i < F; i += 32) s = fmaf(to_float(yv[i]), to_float(w[i]), s);
+        if (VEC) {
+#pragma unroll 2
+            for (int i = lane * 8; i < F; i += 256) {
+                float a[8], b[8];
+                load8(yv + i, a);
+                load8(w + i, b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s = fmaf(a[j], b[j], s);
+            }
+        } else {
+            for (int i = lane; i < F; i += 32) s = fmaf(to_float(yv[i]), to_float(w[i]), s);
+        }
         total += warp_sum(s);
     }
     if (lane == 0) out[(size_t)n * Hd + c] = total;
@@ -123,13 +166,18 @@ LLMP_API int llmp_expert_rows(const void* h, const void* w_gu, const void* w_dow
     LLMP_REQUIRE(top > 0 && Hd > 0 && F > 0, "expert_rows: bad sizes top=%d width=%d ff=%d", top, Hd, F);
     LLMP_REQUIRE((F + 7) / 8 <= 65535 && (Hd + 7) / 8 <= 65535, "expert_rows: too wide");
     dim3 g1(N * top, (F + 7) / 8), g2(N, (Hd + 7) / 8);
-    if (dtype == LLMP_F32) {
-        expert_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, (const float*)w_gu, ids, wts, limit, (float*)y, top, Hd, F);
-        expert_down_kernel<float><<<g2, 256, 0, stream>>>((const float*)y, (const float*)w_down, ids, out, top, Hd, F);
-    } else {
-        expert_gate_up_kernel<bf16><<<g1, 256, 0, stream>>>((const bf16*)h, (const bf16*)w_gu, ids, wts, limit, (bf16*)y, top, Hd, F);
-        expert_down_kernel<bf16><<<g2, 256, 0, stream>>>((const bf16*)y, (const bf16*)w_down, ids, out, top, Hd, F);
-    }
+    const bool aligned = ((size_t)h | (size_t)w_gu | (size_t)w_down | (size_t)y) % 16 == 0;
+    const bool v1 = aligned && Hd % 8 == 0, v2 = aligned && F % 8 == 0;
+#define LLMP_EXPERT_ROWS(T)                                                                                                        \
+    do {                                                                                                                           \
+        if (v1) expert_gate_up_kernel<T, true><<<g1, 256, 0, stream>>>((const T*)h, (const T*)w_gu, ids, wts, limit, (T*)y, top, Hd, F);  \
+        else expert_gate_up_kernel<T, false><<<g1, 256, 0, stream>>>((const T*)h, (const T*)w_gu, ids, wts, limit, (T*)y, top, Hd, F);    \
+        if (v2) expert_down_kernel<T, true><<<g2, 256, 0, stream>>>((const T*)y, (const T*)w_down, ids, out, top, Hd, F);                 \
+        else expert_down_kernel<T, false><<<g2, 256, 0, stream>>>((const T*)y, (const T*)w_down, ids, out, top, Hd, F);                   \
+    } while (0)
+    if (dtype == LLMP_F32) LLMP_EXPERT_ROWS(float);
+    else LLMP_EXPERT_ROWS(bf16);
+#undef LLMP_EXPERT_ROWS
     return llmp_check_launch("expert_rows");
 }
 
