@@ -64,6 +64,12 @@ __device__ __forceinline__ unsigned lm_pack(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
+// The barrier of a key half's four warps: ids 1 and 2 (0 is the block's own).
+__device__ __forceinline__ void lm_half_barrier(int half) {
+    if (half == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+}
+
 template <int LM_VCHUNK>
 __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(const LatentMmaParams p) {
     extern __shared__ __align__(16) unsigned char lm_smem[];
@@ -155,7 +161,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
             }
             key_off[half * 32 + gtid] = off;
         }
-        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+        lm_half_barrier(half);
         for (int e = gtid; e < 32 * vec_per_row; e += 128) {
             const int key = half * 32 + e / vec_per_row, c = (e % vec_per_row) * 8;
             const long long off = key_off[key];
@@ -163,7 +169,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");
+        lm_half_barrier(half);
         do {
             const int jh = j0 + half * 32;
             if (!warp_has_rows || jh > warp_hi_pos || jh > hi) break;      // no row of this warp sees these keys
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
                 }
             }
         } while (false);
-        asm volatile("bar.sync %0, 128;\n" ::"r"(1 + half) : "memory");      // the half's rows may be overwritten now
+        lm_half_barrier(half);      // the half's rows may be overwritten now
     }
 
 #pragma unroll

@@ -8,12 +8,13 @@
 // vector it read, so running it again gives the same result (a captured decode step may be replayed).
 //
 // Since the recurrence is linear in S, S_end = A S_begin + B over any run of tokens, with A = prod(1 - z) and B the
-// run's result from S_begin = 0. Long portions are cut into chunks of SCAN_CHUNK tokens: a first kernel leaves (A, B)
+// run's result from S_begin = 0. Long portions are cut into chunks of SCAN_CHUNK tokens (short ones, so that a
+// prompt of a few thousand tokens gives every SM its fill of warps): a first kernel leaves (A, B)
 // of every chunk, a second one walks the chunks of a request and leaves the state before each, a third one runs the
 // tokens of every chunk from there, so the tokens of a portion run in parallel. Short portions (decode steps) take one kernel that walks its tokens in order.
 #include "common.cuh"
 
-#define SCAN_CHUNK 64
+#define SCAN_CHUNK 32
 
 // 1 / (1 + e^-x) with a correctly rounded reciprocal (one special-function instruction and a fix-up, not a division)
 __device__ __forceinline__ float sigmoidf_(float x) { return __frcp_rn(1.f + expf(-x)); }
