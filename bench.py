@@ -22,6 +22,11 @@ timed region, the greedy tokens of steps of 8 and 64 requests on a two-layer mod
 with the plain implementation. All weights and token ids are synthetic (seeded); the inputs are far
 larger than L2, so no flush is needed between iterations.
 
+``--compare zupilorn [--size 1k|2k]`` leaves the headline aside and puts the Zupilorn hybrid decoder (recurrent and
+latent-attention mixers, dense and routed-expert feed-forwards) at real layer sizes beside a Qwen3 dense decoder of the
+same width, depth and vocabulary: a 2,048-token prompt, decode at ``--batch`` requests of 2,048 tokens, and the device
+time of every kernel class of both, in one JSON line of its own shape.
+
 ``--impl reference`` runs DavidAkinpelu/llm-pipeline's own ``Qwen3ForCausalLM`` from
 ``baseline/_ref`` (installed offline with pip --no-deps --target) with its ``past_key_values``
 loop at the same sizes and prints the same line with ``"impl": "reference"``.

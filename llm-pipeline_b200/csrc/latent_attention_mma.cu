@@ -1,4 +1,4 @@
-// Latent attention on the tensor cores (bfloat16, mma.sync m16n8k16, float32 sums), with the contract of
+// Latent attention on the tensor cores (bfloat16, mma.sync m16n8k16, float32 sums), with the interface of
 // llmp_latent_attention: rows (token, head) attend over cached rows [rank + rot] that all heads share; a cached row is
 // the key, its first `rank` entries are the value.
 //
