@@ -8,6 +8,8 @@ the same ``group_key()`` share page ids and block tables. The manager, the memor
 benchmark read sizes from the spec alone (``elements_per_token``, ``bytes_per_token``).
 
 * ``KVPagesSpec``: keys and values of attention, page ``[2, kv_heads, page_size, head_dim]``.
+* ``HeadRowPagesSpec``: one row of ``row_size`` entries per key/value head and token (keys and values of different
+  widths, or several keys, packed side by side), page ``[kv_heads, page_size, row_size]``.
 * ``TokenPagesSpec``: any payload of a fixed shape per token, page ``[page_size, *token_shape]``
   (a latent vector, keys and values of different widths packed side by side, ...).
 
@@ -57,6 +59,16 @@ class KVPagesSpec(PagesSpec):
 
     def group_key(self):
         return ("kv", self.num_kv_heads, self.head_dim, self.window)
+
+
+@dataclass(frozen=True)
+class HeadRowPagesSpec(PagesSpec):
+    num_kv_heads: int
+    row_size: int
+    window: Optional[int] = None
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return (self.num_kv_heads, page_size, self.row_size)
 
 
 @dataclass(frozen=True)

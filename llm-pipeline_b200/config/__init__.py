@@ -5,7 +5,8 @@ from .registry import (architecture_name, load_config, register_architecture, re
                        supported_architectures)
 from .qwen3 import Qwen3Config
 from .zupilorn import ZupilornConfig
+from .razelorn import RazelornConfig
 
-__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "ZupilornConfig",
+__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "ZupilornConfig", "RazelornConfig",
            "architecture_name", "load_config", "register_architecture", "resolve_config",
            "supported_architectures"]

@@ -8,17 +8,17 @@
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int H, int V) {
+                                 float* __restrict__ out, int H, int V, float scale) {
     const int n = blockIdx.x;
     const int id = ids[n];
     const bool ok = id >= 0 && id < V;
     const T* row = table + (size_t)(ok ? id : 0) * H;
     float* dst = out + (size_t)n * H;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H; c += gridDim.y * blockDim.x)
-        dst[c] = ok ? to_float(row[c]) : 0.f;
+        dst[c] = ok ? to_float(row[c]) * scale : 0.f;
 }
 
-LLMP_API int llmp_embedding(const int* ids, const void* table, int dtype, float* out, int N, int H, int V,
+LLMP_API int llmp_embedding(const int* ids, const void* table, int dtype, float* out, int N, int H, int V, float scale,
                             cudaStream_t stream) {
     if (N <= 0) return 0;
     LLMP_REQUIRE(H > 0 && V > 0, "embedding: bad sizes H=%d V=%d", H, V);
@@ -27,9 +27,9 @@ LLMP_API int llmp_embedding(const int* ids, const void* table, int dtype, float*
     if ((long)N * col_blocks > 4096) col_blocks = 1;
     dim3 grid(N, col_blocks);
     if (dtype == LLMP_F32)
-        embedding_kernel<float><<<grid, threads, 0, stream>>>(ids, (const float*)table, out, H, V);
+        embedding_kernel<float><<<grid, threads, 0, stream>>>(ids, (const float*)table, out, H, V, scale);
     else
-        embedding_kernel<bf16><<<grid, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V);
+        embedding_kernel<bf16><<<grid, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V, scale);
     return llmp_check_launch("embedding");
 }
 

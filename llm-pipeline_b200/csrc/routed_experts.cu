@@ -1,25 +1,35 @@
 // A feed-forward of many small experts of which every token uses a few.
-//   route_topk:      router logits in float32 (float32 copy of the router matrix, the token's row as stored), sigmoid
-//                    scores, the `top` largest; a chosen expert's weight is its score.
-//   expert_gate_up:  per (token, choice): g = min(w (Wg h), limit), u = clamp(w (Wu h), -limit, limit),
-//                    y = g sigmoid(1.702 g) (u + 1). The weight scales the expert's input; as the first products are
-//                    linear, it is applied to their float32 sums instead.
-//   expert_down:     out[token] = sum over the token's choices, in their order, of Wd y (float32).
+//   route_topk:      router logits in float32 (float32 copy of the router matrix, the token's row as stored); scores by
+//                    sigmoid (each logit alone) or softmax (over all router outputs); the `top` largest of
+//                    score (+ a correction per router output, if given); a chosen expert's weight is its score
+//                    without the correction. A further row of the matrix, if asked for, gives a gate per token:
+//                    sigmoid of its logit.
+//   expert_gate_up:  per (token, choice), with w the choice's weight, by the form of the expert:
+//                    clamped:  g = min(w (Wg h), limit), u = clamp(w (Wu h), -limit, limit), y = g sigmoid(1.702 g) (u + 1)
+//                              (the weight scales the expert's input; the first products are linear, so it is applied to
+//                              their float32 sums);
+//                    silu:     y = w silu(Wg h) (Wu h) (the weight scales the expert's output; the last product is
+//                              linear, so it is applied to the float32 activation before it is rounded).
+//   expert_down:     out[token] = sum over the token's choices, in their order, of Wd y (float32). A choice whose id is
+//                    not below the number of experts with matrices is an identity expert: it adds w h.
 // These kernels read an expert's rows once per token that chose it (a warp per output row): the form for the few
 // rows of a decode step. Steps with many rows sort their (token, choice) pairs by expert and take the grouped
 // product further down, which reads an expert's rows once per 64 pairs.
 #include "common.cuh"
 
 __global__ void route_topk_kernel(const void* __restrict__ h, int h_bf16, const float* __restrict__ wr, int top, int* __restrict__ ids,
-                                  float* __restrict__ wts, int Hd, int E) {
+                                  float* __restrict__ wts, int Hd, int E, int softmax, const float* __restrict__ correction,
+                                  float* __restrict__ gate) {
     extern __shared__ float route_smem[];
-    float* logits = route_smem;                              // [E]
-    float* row = route_smem + E;                             // [Hd]: the token's row, read once
+    float* logits = route_smem;                              // [E + 1]: logits, then what the choice goes by
+    float* score = route_smem + E + 1;                       // [E]: softmax scores (softmax only)
+    float* row = route_smem + 2 * E + 1;                     // [Hd]: the token's row, read once
+    const int rows_w = gate ? E + 1 : E;                     // the gate's row follows the experts' rows
     const int n = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     for (int i = threadIdx.x; i < Hd; i += blockDim.x) row[i] = load_as_float(h, h_bf16, (size_t)n * Hd + i);
     __syncthreads();
-    for (int e = warp; e < E; e += nwarps) {
+    for (int e = warp; e < rows_w; e += nwarps) {
         const float* w = wr + (size_t)e * Hd;
         // eight sums a lane, so that eight loads are in flight; their order of addition is fixed
         float acc[8];
@@ -36,6 +46,33 @@ __global__ void route_topk_kernel(const void* __restrict__ h, int h_bf16, const 
     }
     __syncthreads();
     if (warp == 0) {
+        if (gate && lane == 0) gate[n] = 1.f / (1.f + expf(-logits[E]));
+        if (softmax) {
+            float mx = -INFINITY;
+            for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logits[e]);
+            mx = warp_max(mx);
+            float sum = 0.f;
+            for (int e = lane; e < E; e += 32) {
+                const float p = expf(logits[e] - mx);
+                score[e] = p;
+                sum += p;
+            }
+            sum = warp_sum(sum);
+            __syncwarp();
+            for (int e = lane; e < E; e += 32) {
+                const float p = score[e] / sum;
+                score[e] = p;
+                logits[e] = correction ? p + correction[e] : p;
+            }
+            __syncwarp();
+        } else if (correction) {
+            for (int e = lane; e < E; e += 32) {
+                score[e] = 1.f / (1.f + expf(-logits[e]));
+                logits[e] = score[e] + correction[e];
+            }
+            __syncwarp();
+        }
+        const bool by_score = softmax || correction;
         for (int k = 0; k < top; ++k) {
             float best = -INFINITY;
             int at = -1;
@@ -48,7 +85,7 @@ __global__ void route_topk_kernel(const void* __restrict__ h, int h_bf16, const 
             }
             if (lane == 0) {
                 ids[(size_t)n * top + k] = at;
-                wts[(size_t)n * top + k] = 1.f / (1.f + expf(-best));
+                wts[(size_t)n * top + k] = by_score ? score[at] : 1.f / (1.f + expf(-best));
                 logits[at] = -INFINITY;
             }
             __syncwarp();
@@ -56,19 +93,24 @@ __global__ void route_topk_kernel(const void* __restrict__ h, int h_bf16, const 
     }
 }
 
+// softmax: 0 sigmoid scores, 1 softmax over the E router outputs. correction: float32 [E] or null. gate: float32 [N] or
+// null; when given, w_router has E + 1 rows and gate[n] = sigmoid(row E . h[n]).
 LLMP_API int llmp_route_topk(const void* h, int h_dtype, const float* w_router, int top, int* ids, float* wts, int N, int Hd, int E,
-                             cudaStream_t stream) {
+                             int softmax, const float* correction, float* gate, cudaStream_t stream) {
     if (N <= 0) return 0;
     LLMP_REQUIRE(E > 0 && top > 0 && top <= E && Hd > 0 && E <= 8192, "route_topk: bad sizes experts=%d top=%d width=%d", E, top, Hd);
-    const size_t smem = (size_t)(E + Hd) * sizeof(float);
+    const size_t smem = (size_t)(2 * E + 1 + Hd) * sizeof(float);
     LLMP_REQUIRE(smem <= 200 * 1024, "route_topk: a row of %d entries does not fit shared memory", Hd);
     LLMP_ALLOW_SMEM(route_topk_kernel, smem);
     // few rows (a decode step): a warp per expert, so that the router matrix is read by many warps at once
-    route_topk_kernel<<<N, N <= 64 ? 1024 : 256, smem, stream>>>(h, h_dtype == LLMP_BF16, w_router, top, ids, wts, Hd, E);
+    route_topk_kernel<<<N, N <= 64 ? 1024 : 256, smem, stream>>>(h, h_dtype == LLMP_BF16, w_router, top, ids, wts, Hd, E, softmax,
+                                                                  correction, gate);
     return llmp_check_launch("route_topk");
 }
 
-__device__ __forceinline__ float expert_act(float g, float u, float w, float limit) {
+// form 0: clamped, the weight on the input; form 1: silu(g) u, the weight on the output
+__device__ __forceinline__ float expert_act(float g, float u, float w, float limit, int form) {
+    if (form == 1) return w * (g / (1.f + expf(-g))) * u;
     g = fminf(w * g, limit);
     u = fminf(fmaxf(w * u, -limit), limit);
     return g * (1.f / (1.f + expf(-1.702f * g))) * (u + 1.f);
@@ -94,12 +136,14 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
 // VEC: the rows' length is a multiple of 8; a lane then takes 8 consecutive entries a step, in 16-byte loads.
 template <typename T, bool VEC>
 __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ ids,
-                                      const float* __restrict__ wts, float limit, T* __restrict__ y, int top, int Hd, int F) {
+                                      const float* __restrict__ wts, float limit, T* __restrict__ y, int top, int Hd, int F,
+                                      int form, int E) {
     const int pair = blockIdx.x;
     const int f = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (f >= F) return;
     const int e = ids[pair];
+    if (e >= E) return;                                      // an identity expert has no matrices
     const T* x = h + (size_t)(pair / top) * Hd;
     const T* wg = w_gu + ((size_t)e * 2 * F + f) * Hd;
     const T* wu = wg + (size_t)F * Hd;
@@ -126,13 +170,14 @@ __global__ void expert_gate_up_kernel(const T* __restrict__ h, const T* __restri
     }
     g = warp_sum(g);
     u = warp_sum(u);
-    if (lane == 0) y[(size_t)pair * F + f] = from_float<T>(expert_act(g, u, wts[pair], limit));
+    if (lane == 0) y[(size_t)pair * F + f] = from_float<T>(expert_act(g, u, wts[pair], limit, form));
 }
 
 // grid (tokens, ceil(Hd / 8)): a warp per output entry, the token's choices added in their order.
 template <typename T, bool VEC>
 __global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict__ w_down, const int* __restrict__ ids,
-                                   float* __restrict__ out, int top, int Hd, int F) {
+                                   float* __restrict__ out, int top, int Hd, int F, const T* __restrict__ h,
+                                   const float* __restrict__ wts, int E) {
     const int n = blockIdx.x;
     const int c = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -140,6 +185,10 @@ __global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict_
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         const int pair = n * top + k;
+        if (ids[pair] >= E) {                                // identity expert: the weighted input itself
+            total += wts[pair] * to_float(h[(size_t)n * Hd + c]);
+            continue;
+        }
         const T* w = w_down + ((size_t)ids[pair] * Hd + c) * F;
         const T* yv = y + (size_t)pair * F;
         float s = 0.f;
@@ -160,8 +209,9 @@ __global__ void expert_down_kernel(const T* __restrict__ y, const T* __restrict_
     if (lane == 0) out[(size_t)n * Hd + c] = total;
 }
 
+// form: the expert's form (expert_act). E: experts with matrices; ids from E on are identity experts.
 LLMP_API int llmp_expert_rows(const void* h, const void* w_gu, const void* w_down, int dtype, const int* ids, const float* wts,
-                              float limit, void* y, float* out, int N, int top, int Hd, int F, cudaStream_t stream) {
+                              float limit, void* y, float* out, int N, int top, int Hd, int F, int form, int E, cudaStream_t stream) {
     if (N <= 0) return 0;
     LLMP_REQUIRE(top > 0 && Hd > 0 && F > 0, "expert_rows: bad sizes top=%d width=%d ff=%d", top, Hd, F);
     LLMP_REQUIRE((F + 7) / 8 <= 65535 && (Hd + 7) / 8 <= 65535, "expert_rows: too wide");
@@ -170,10 +220,10 @@ LLMP_API int llmp_expert_rows(const void* h, const void* w_gu, const void* w_dow
     const bool v1 = aligned && Hd % 8 == 0, v2 = aligned && F % 8 == 0;
 #define LLMP_EXPERT_ROWS(T)                                                                                                        \
     do {                                                                                                                           \
-        if (v1) expert_gate_up_kernel<T, true><<<g1, 256, 0, stream>>>((const T*)h, (const T*)w_gu, ids, wts, limit, (T*)y, top, Hd, F);  \
-        else expert_gate_up_kernel<T, false><<<g1, 256, 0, stream>>>((const T*)h, (const T*)w_gu, ids, wts, limit, (T*)y, top, Hd, F);    \
-        if (v2) expert_down_kernel<T, true><<<g2, 256, 0, stream>>>((const T*)y, (const T*)w_down, ids, out, top, Hd, F);                 \
-        else expert_down_kernel<T, false><<<g2, 256, 0, stream>>>((const T*)y, (const T*)w_down, ids, out, top, Hd, F);                   \
+        if (v1) expert_gate_up_kernel<T, true><<<g1, 256, 0, stream>>>((const T*)h, (const T*)w_gu, ids, wts, limit, (T*)y, top, Hd, F, form, E);  \
+        else expert_gate_up_kernel<T, false><<<g1, 256, 0, stream>>>((const T*)h, (const T*)w_gu, ids, wts, limit, (T*)y, top, Hd, F, form, E);    \
+        if (v2) expert_down_kernel<T, true><<<g2, 256, 0, stream>>>((const T*)y, (const T*)w_down, ids, out, top, Hd, F, (const T*)h, wts, E);                 \
+        else expert_down_kernel<T, false><<<g2, 256, 0, stream>>>((const T*)y, (const T*)w_down, ids, out, top, Hd, F, (const T*)h, wts, E);                   \
     } while (0)
     if (dtype == LLMP_F32) LLMP_EXPERT_ROWS(float);
     else LLMP_EXPERT_ROWS(bf16);
@@ -198,9 +248,10 @@ LLMP_API int llmp_expert_rows(const void* h, const void* w_gu, const void* w_dow
 #define GX_K 64
 #define GX_STRIDE (GX_K + 8)
 
-__global__ void moe_count_kernel(const int* __restrict__ ids, int pairs, int* __restrict__ counts) {
+// pairs of identity experts (ids from E on) take no part in the sorted order
+__global__ void moe_count_kernel(const int* __restrict__ ids, int pairs, int* __restrict__ counts, int E) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < pairs) atomicAdd(&counts[ids[i]], 1);
+    if (i < pairs && ids[i] < E) atomicAdd(&counts[ids[i]], 1);
 }
 
 // One block. counts[E] -> cursor[E] (first sorted row of each expert), the tile list and its length.
@@ -221,9 +272,9 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __re
     *num_tiles = tiles;
 }
 
-__global__ void moe_scatter_kernel(const int* __restrict__ ids, int pairs, int* __restrict__ cursor, int* __restrict__ sorted_pair) {
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, int pairs, int* __restrict__ cursor, int* __restrict__ sorted_pair, int E) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < pairs) sorted_pair[atomicAdd(&cursor[ids[i]], 1)] = i;
+    if (i < pairs && ids[i] < E) sorted_pair[atomicAdd(&cursor[ids[i]], 1)] = i;
 }
 
 __device__ __forceinline__ void gx_cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
@@ -251,7 +302,7 @@ struct GroupedArgs {
     const float* wts;
     bf16* y;                  // first product's result [sorted rows, cols_total]
     float* out;               // second product's result [pairs, cols_total]
-    int top, K, cols_total;
+    int top, K, cols_total, form;
     float limit;
 };
 
@@ -340,19 +391,23 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const GroupedArgs a) {
             for (int c2 = 0; c2 < 2; ++c2) {
                 const int col = col0 + nb * 8 + 2 * t + c2;
                 if (col >= a.cols_total) continue;
-                if (GATED) a.y[(size_t)(row0 + row) * a.cols_total + col] = __float2bfloat16_rn(expert_act(cg[nb][2 * h2 + c2], cu[GATED ? nb : 0][2 * h2 + c2], w, a.limit));
+                if (GATED) a.y[(size_t)(row0 + row) * a.cols_total + col] = __float2bfloat16_rn(expert_act(cg[nb][2 * h2 + c2], cu[GATED ? nb : 0][2 * h2 + c2], w, a.limit, a.form));
                 else a.out[(size_t)pair * a.cols_total + col] = cg[nb][2 * h2 + c2];
             }
         }
     }
 }
 
-__global__ void moe_combine_kernel(const float* __restrict__ pair_out, float* __restrict__ out, int top, int Hd, size_t total) {
+__global__ void moe_combine_kernel(const float* __restrict__ pair_out, float* __restrict__ out, int top, int Hd, size_t total,
+                                   const int* __restrict__ ids, const float* __restrict__ wts, const bf16* __restrict__ h, int E) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t n = i / Hd, c = i % Hd;
     float s = 0.f;
-    for (int k = 0; k < top; ++k) s += pair_out[(n * top + k) * Hd + c];
+    for (int k = 0; k < top; ++k) {
+        const size_t pair = n * top + k;
+        s += ids[pair] < E ? pair_out[pair * Hd + c] : wts[pair] * __bfloat162float(h[i]);     // identity expert: w h
+    }
     out[i] = s;
 }
 
@@ -362,10 +417,11 @@ LLMP_API int llmp_expert_grouped_supports(int Hd, int F) { return Hd % 8 == 0 &&
 LLMP_API long llmp_expert_grouped_rows(int pairs, int E) { return ((long)(pairs + GX_ROWS - 1) / GX_ROWS + E) * GX_ROWS; }
 
 // ints: int32 scratch [3 E + 1 + 2 tiles_max + rows_max] with tiles_max = rows_max / 64; y: bf16 [rows_max, F];
-// pair_out: float32 [pairs, Hd] (unused when top == 1: the rows go straight to out).
+// pair_out: float32 [pairs, Hd] (unused when top == 1 and there are no identity experts: the rows go straight to out).
+// form: the expert's form (expert_act). identity: ids E .. E + identity - 1 are identity experts.
 LLMP_API int llmp_expert_grouped(const void* h, const void* w_gu, const void* w_down, const int* ids, const float* wts, float limit,
-                                 int* ints, void* y, float* pair_out, float* out, int N, int top, int Hd, int F, int E,
-                                 cudaStream_t stream) {
+                                 int* ints, void* y, float* pair_out, float* out, int N, int top, int Hd, int F, int E, int form,
+                                 int identity, cudaStream_t stream) {
     if (N <= 0) return 0;
     LLMP_REQUIRE(llmp_expert_grouped_supports(Hd, F) && top > 0 && E > 0, "expert_grouped: sizes width=%d ff=%d are not served", Hd, F);
     const int pairs = N * top;
@@ -379,22 +435,24 @@ LLMP_API int llmp_expert_grouped(const void* h, const void* w_gu, const void* w_
     int* sorted_pair = tile_row0 + tiles_max;
     cudaMemsetAsync(counts, 0, sizeof(int) * E, stream);
     cudaMemsetAsync(sorted_pair, 0xFF, sizeof(int) * rows_max, stream);
-    moe_count_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, counts);
+    moe_count_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, counts, E);
     moe_plan_kernel<<<1, 32, 0, stream>>>(counts, E, cursor, tile_expert, tile_row0, num_tiles);
-    moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, cursor, sorted_pair);
+    moe_scatter_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, pairs, cursor, sorted_pair, E);
     GroupedArgs a;
     a.sorted_pair = sorted_pair; a.tile_expert = tile_expert; a.tile_row0 = tile_row0; a.num_tiles = num_tiles;
-    a.wts = wts; a.y = (bf16*)y; a.top = top; a.limit = limit;
+    a.wts = wts; a.y = (bf16*)y; a.top = top; a.limit = limit; a.form = form;
+    const bool combine = top > 1 || identity > 0;
+    LLMP_REQUIRE(!combine || pair_out, "expert_grouped: the sum over a token's choices needs its scratch");
     a.a = (const bf16*)h; a.w = (const bf16*)w_gu; a.K = Hd; a.cols_total = F; a.out = nullptr;
     const size_t smem_gated = sizeof(bf16) * 2 * 3 * GX_ROWS * GX_STRIDE, smem_plain = sizeof(bf16) * 2 * 2 * GX_ROWS * GX_STRIDE;
     LLMP_ALLOW_SMEM(moe_grouped_kernel<true>, smem_gated);
     moe_grouped_kernel<true><<<dim3(tiles_max, (F + GX_COLS - 1) / GX_COLS), 128, smem_gated, stream>>>(a);
-    a.a = (const bf16*)y; a.w = (const bf16*)w_down; a.K = F; a.cols_total = Hd; a.out = top == 1 ? out : pair_out;
+    a.a = (const bf16*)y; a.w = (const bf16*)w_down; a.K = F; a.cols_total = Hd; a.out = combine ? pair_out : out;
     LLMP_ALLOW_SMEM(moe_grouped_kernel<false>, smem_plain);
     moe_grouped_kernel<false><<<dim3(tiles_max, (Hd + GX_COLS - 1) / GX_COLS), 128, smem_plain, stream>>>(a);
-    if (top > 1) {
+    if (combine) {
         const size_t total = (size_t)N * Hd;
-        moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(pair_out, out, top, Hd, total);
+        moe_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(pair_out, out, top, Hd, total, ids, wts, (const bf16*)h, E);
     }
     return llmp_check_launch("expert_grouped");
 }

@@ -36,7 +36,7 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 _SIGNATURES = {
-    "llmp_embedding": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "llmp_embedding": [_P, _P, _I, _P, _I, _I, _I, _F, _P],
     "llmp_rope_tables": [_P, _P, _F, _P, _P, _I, _I, _P],
     "llmp_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _F, _P, _I, _P, _I, _I, _P],
     "llmp_qkv_post": [_P, _I, _P, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
@@ -67,9 +67,16 @@ _SIGNATURES = {
     "llmp_latent_attention": [_P, _L, _L, _P, _L, _L, _P, _I, _P, _I, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P],
     "llmp_latent_attention_mma": [_P, _L, _L, _P, _L, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I, _F, _I,
                                   _I, _P, _P],
-    "llmp_route_topk": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _P],
-    "llmp_expert_grouped": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
-    "llmp_expert_rows": [_P, _P, _P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _P],
+    "llmp_route_topk": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+    "llmp_expert_grouped": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "llmp_expert_rows": [_P, _P, _P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "llmp_add_layernorm": [_P, _P, _I, _P, _I, _P, _P, _I, _F, _P, _I, _I, _I, _P, _P],
+    "llmp_relu_squared": [_P, _P, _I, _L, _P],
+    "llmp_add_scaled_rows": [_P, _P, _I, _P, _I, _I, _P],
+    "llmp_diff_qkv_post": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, _I, _I, _P],
+    "llmp_diff_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P],
+    "llmp_diff_attention_mma": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F,
+                                _I, _I, _P, _P],
 }
 _bound = {}
 launch_count = 0   # kernels of this library launched so far (captured launches count once per capture)
@@ -171,14 +178,14 @@ def attention_counters(device: torch.device, count: int) -> torch.Tensor:
     return counters
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[n, :] = float32(table[ids[n], :])"""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[n, :] = float32(table[ids[n], :]) * scale"""
     _i32(ids, "ids")
     _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be a contiguous matrix")
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (ids.numel(), table.shape[1]),
           "embedding output must be float32 [tokens, hidden]")
     _call("llmp_embedding", _ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out), ids.numel(),
-          table.shape[1], table.shape[0], _stream())
+          table.shape[1], table.shape[0], float(scale), _stream())
     return out
 
 
@@ -882,20 +889,34 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tens
     return out
 
 
-def route_topk(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
-    """ids[n, :], weights[n, :] = the ``top`` experts with the largest sigmoid(w_router h[n]) and those scores; float32 logits."""
+def route_topk(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, *,
+               softmax: bool = False, correction: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+    """ids[n, :], weights[n, :] = the ``top`` router outputs with the largest score (+ ``correction``, if given) and their
+    scores without the correction; float32 logits. The score is sigmoid(logit), or with ``softmax`` the softmax over all
+    router outputs. With ``gate`` (float32 [tokens]) the matrix has one row more than router outputs, and
+    gate[n] = sigmoid(that row . h[n])."""
     N, Hd = h.shape
-    E = w_router.shape[0]
+    E = w_router.shape[0] - (1 if gate is not None else 0)
     _need(h.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == Hd,
           "the router matrix must be float32 [experts, width]")
     _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (N, top) and weights.dtype == torch.float32 and
           weights.is_contiguous() and weights.shape == (N, top), "route_topk outputs must be int32 and float32 [tokens, top]")
-    _call("llmp_route_topk", _ptr(h), dtype_code(h.dtype), _ptr(w_router), int(top), _ptr(ids), _ptr(weights), N, Hd, E, _stream())
+    if correction is not None:
+        _need(correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == E,
+              "the router's correction must be float32 [router outputs]")
+    if gate is not None:
+        _need(gate.dtype == torch.float32 and gate.is_contiguous() and gate.numel() == N, "the gate must be float32 [tokens]")
+    _call("llmp_route_topk", _ptr(h), dtype_code(h.dtype), _ptr(w_router), int(top), _ptr(ids), _ptr(weights), N, Hd, E,
+          1 if softmax else 0, _ptr(correction), _ptr(gate), _stream())
+
+
+EXPERT_FORMS = {"clamped": 0, "silu": 1}     # csrc/routed_experts.cu: expert_act
 
 
 def expert_rows(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                limit: float, out: torch.Tensor) -> torch.Tensor:
-    """out[n] = sum_k Wd[e] act(weights[n, k] * (Wg[e] h[n]), weights[n, k] * (Wu[e] h[n])) with e = ids[n, k], float32.
+                limit: float, out: torch.Tensor, form: str = "clamped") -> torch.Tensor:
+    """out[n] = sum_k Wd[e] act(Wg[e] h[n], Wu[e] h[n], weights[n, k]) with e = ids[n, k], float32; ``form`` names the
+    activation and where the weight enters (``EXPERT_FORMS``); an id from the number of experts on adds weights[n, k] h[n].
     ``w_gate_up`` [experts, 2 ff, width] (gate rows, then up rows), ``w_down`` [experts, width, ff]. Reads an expert once
     per token that chose it: for the few rows of a decode step."""
     N, Hd = h.shape
@@ -907,7 +928,7 @@ def expert_rows(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (N, Hd), "expert output must be float32 [tokens, width]")
     y = torch.empty((N * top, F), dtype=h.dtype, device=h.device)
     _call("llmp_expert_rows", _ptr(h), _ptr(w_gate_up), _ptr(w_down), dtype_code(h.dtype), _ptr(ids), _ptr(weights), float(limit),
-          _ptr(y), _ptr(out), N, top, Hd, F, _stream())
+          _ptr(y), _ptr(out), N, top, Hd, F, EXPERT_FORMS[form], E, _stream())
     return out
 
 
@@ -924,7 +945,7 @@ def expert_grouped_supports(dtype: torch.dtype, Hd: int, F: int) -> bool:
 
 
 def expert_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                   limit: float, out: torch.Tensor) -> torch.Tensor:
+                   limit: float, out: torch.Tensor, form: str = "clamped", identity: int = 0) -> torch.Tensor:
     """``expert_rows`` for many rows (bfloat16): the pairs are sorted by expert on the device and the experts' products
     run as grouped tensor-core products that read an expert's rows once per 64 pairs."""
     N, Hd = h.shape
@@ -940,20 +961,20 @@ def expert_grouped(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tenso
     rows = int(fn(N * top, E))
     ints = torch.empty(3 * E + 1 + 2 * (rows // 64) + rows, dtype=torch.int32, device=h.device)
     y = torch.empty((rows, F), dtype=torch.bfloat16, device=h.device)
-    pair_out = torch.empty((N * top, Hd), dtype=torch.float32, device=h.device) if top > 1 else None
+    pair_out = torch.empty((N * top, Hd), dtype=torch.float32, device=h.device) if top > 1 or identity else None
     _call("llmp_expert_grouped", _ptr(h), _ptr(w_gate_up), _ptr(w_down), _ptr(ids), _ptr(weights), float(limit), _ptr(ints), _ptr(y),
-          _ptr(pair_out), _ptr(out), N, top, Hd, F, E, _stream())
+          _ptr(pair_out), _ptr(out), N, top, Hd, F, E, EXPERT_FORMS[form], int(identity), _stream())
     return out
 
 
 def routed_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                   limit: float, out: torch.Tensor) -> torch.Tensor:
+                   limit: float, out: torch.Tensor, form: str = "clamped", identity: int = 0) -> torch.Tensor:
     """The experts' work for a step's rows, by the kernel that suits their number: grouped tensor-core products for many
     bfloat16 rows, a warp per output entry (``expert_rows``) for the few rows of a decode step and for float32."""
     pairs = ids.numel()
     if pairs >= EXPERT_GROUPED_MIN_ROWS and expert_grouped_supports(h.dtype, h.shape[1], w_down.shape[2]):
-        return expert_grouped(h, w_gate_up, w_down, ids, weights, limit, out)
-    return expert_rows(h, w_gate_up, w_down, ids, weights, limit, out)
+        return expert_grouped(h, w_gate_up, w_down, ids, weights, limit, out, form, identity)
+    return expert_rows(h, w_gate_up, w_down, ids, weights, limit, out, form)
 
 
 LATENT_SEGMENT_KEYS = 256            # keys per segment when a step's rows are too few to fill the GPU (a multiple of the key tile)
@@ -1000,4 +1021,136 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.
           _ptr(pages), _ptr(tables), tables.shape[1], _ptr(q_start), _ptr(ctx_len), _ptr(positions), _ptr(tile_req), _ptr(tile_tok0),
           tile_req.numel(), _ptr(out), out.stride(0), out.stride(1), N, H, rank, rot, pages.shape[1], float(scale),
           LATENT_SEGMENT_KEYS if segments > 0 else 0, int(segments), _ptr(scratch), _stream())
+    return out
+
+
+def add_layernorm(residual: torch.Tensor, delta: Optional[torch.Tensor], delta2: Optional[torch.Tensor], weight: torch.Tensor,
+                  bias: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += delta + delta2 (float32, in place; either may be None), then out = layer norm of the rows with ``weight``
+    and ``bias`` (variance = mean of the squared deviations), float32 statistics. With ``rows`` only those rows are normed
+    into ``out`` and the residual is left as it is."""
+    R, H = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "the residual must be contiguous float32")
+    for d in (delta, delta2):
+        if d is not None:
+            _need(d.shape == residual.shape and d.is_contiguous(), "an addend must have the residual's shape")
+            dtype_code(d.dtype)
+    _need(weight.numel() == H and bias.numel() == H and weight.dtype == bias.dtype and weight.is_contiguous() and bias.is_contiguous(),
+          "layer norm weight and bias must have the row's length and one type")
+    count = R
+    if rows is not None:
+        _i32(rows, "rows")
+        count = rows.numel()
+    _need(out.shape == (count, H) and out.is_contiguous(), "layer norm output has the wrong shape")
+    _call("llmp_add_layernorm", _ptr(residual), _ptr(delta), dtype_code(delta.dtype) if delta is not None else F32, _ptr(delta2),
+          dtype_code(delta2.dtype) if delta2 is not None else F32, _ptr(weight), _ptr(bias), dtype_code(weight.dtype), float(eps),
+          _ptr(out), dtype_code(out.dtype), count, H, _ptr(rows), _stream())
+    return out
+
+
+def relu_squared(z: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = max(z, 0)^2"""
+    _need(z.is_contiguous() and out.is_contiguous() and z.shape == out.shape and z.dtype == out.dtype, "relu_squared shapes do not match")
+    _call("llmp_relu_squared", _ptr(z), _ptr(out), dtype_code(z.dtype), z.numel(), _stream())
+    return out
+
+
+def add_scaled_rows(out: torch.Tensor, x: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """out[n, :] += scales[n] * x[n, :] (float32 ``out`` and ``scales``)."""
+    N, H = out.shape
+    _need(out.dtype == torch.float32 and out.is_contiguous() and x.shape == out.shape and x.is_contiguous() and
+          scales.dtype == torch.float32 and scales.is_contiguous() and scales.numel() == N, "add_scaled_rows shapes do not match")
+    _call("llmp_add_scaled_rows", _ptr(out), _ptr(x), dtype_code(x.dtype), _ptr(scales), N, H, _stream())
+    return out
+
+
+def diff_qkv_post(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, vdim: int, q_weight: torch.Tensor,
+                  k_weight: torch.Tensor, eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                  slots: Optional[torch.Tensor], pages: Optional[torch.Tensor]) -> None:
+    """In place on ``qkv`` [tokens, heads 2 dim | kv_heads 2 dim | kv_heads vdim] (two maps per head): every run of ``dim``
+    entries of q and k is RMS-normed with ``q_weight`` / ``k_weight`` and its first ``rotary_dim`` entries rotated; q stays
+    in place, k and v go to the token's slot of ``pages`` [pages, kv_heads, page_size, 2 dim + vdim]."""
+    N = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] == 2 * dim * (num_heads + num_kv_heads) + num_kv_heads * vdim,
+          "diff_qkv_post: the product has the wrong width")
+    _need(q_weight.numel() == dim and k_weight.numel() == dim and q_weight.dtype == k_weight.dtype and q_weight.is_contiguous() and
+          k_weight.is_contiguous(), "q/k norm weights must have the key size and one type")
+    if rotary_dim:
+        _need(cos is not None and sin is not None and cos.shape == (N, rotary_dim // 2) and cos.dtype == torch.float32 and
+              cos.is_contiguous() and sin.is_contiguous(), "rotary tables must be float32 [tokens, rotated / 2]")
+    page_size = 0
+    if pages is not None:
+        _need(pages.dtype == qkv.dtype and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1] == num_kv_heads and
+              pages.shape[3] == 2 * dim + vdim and slots is not None, "differential attention pages have the wrong layout")
+        _i32(slots, "slots")
+        page_size = pages.shape[2]
+    _call("llmp_diff_qkv_post", _ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0), num_heads, num_kv_heads, dim, vdim, _ptr(q_weight),
+          _ptr(k_weight), dtype_code(q_weight.dtype), float(eps), _ptr(cos), _ptr(sin), int(rotary_dim),
+          _ptr(slots) if pages is not None else None, _ptr(pages), page_size, N, _stream())
+
+
+def diff_attention(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, token_request: torch.Tensor, positions: torch.Tensor,
+                   out: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, vdim: int, window: int, scale: float, lam: float,
+                   eps: float, out_scale: float) -> torch.Tensor:
+    """Differential attention of rows (token, head), any sizes, float32 or bfloat16: ``q`` [tokens, >= heads 2 dim] (a view
+    with a dense last axis; head h's two queries at h 2 dim), ``pages`` [pages, kv_heads, page_size, 2 dim + vdim], ``out``
+    [tokens, heads vdim] = rms_norm(a1 - lam a2) * out_scale per head, with a1, a2 the two maps' softmax-weighted sums of
+    the values; ``window`` > 0: a token sees itself and the window - 1 tokens before it."""
+    N = q.shape[0]
+    _need(q.stride(1) == 1 and q.shape[1] >= 2 * dim * num_heads and out.shape == (N, num_heads * vdim) and out.stride(1) == 1,
+          "differential attention shapes do not match")
+    _need(q.dtype == pages.dtype == out.dtype, "differential attention operands must have one type")
+    _need(pages.is_contiguous() and pages.dim() == 4 and pages.shape[1] == num_kv_heads and pages.shape[3] == 2 * dim + vdim,
+          "differential attention pages have the wrong layout")
+    _i32(tables, "tables"); _i32(token_request, "token_request"); _i32(positions, "positions")
+    _call("llmp_diff_attention", _ptr(q), q.stride(0), _ptr(pages), dtype_code(pages.dtype), _ptr(tables), tables.shape[1],
+          _ptr(token_request), _ptr(positions), _ptr(out), out.stride(0), N, num_heads, num_kv_heads, dim, vdim, pages.shape[2],
+          int(window), float(scale), float(lam), float(eps), float(out_scale), _stream())
+    return out
+
+
+DIFF_SEGMENT_KEYS = 256              # keys per segment when a step's rows are too few to fill the GPU (a multiple of the key tile)
+
+
+def diff_mma_supports(dtype: torch.dtype, dim: int, vdim: int, page_size: int) -> bool:
+    """Whether the tensor-core differential attention kernel serves these sizes (bfloat16)."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = library().llmp_diff_mma_supports
+    fn.argtypes = [_I, _I, _I]
+    fn.restype = _I
+    return bool(fn(dim, vdim, page_size))
+
+
+def diff_mma_tokens_per_tile(num_heads: int, num_kv_heads: int) -> int:
+    fn = library().llmp_diff_mma_tokens_per_tile
+    fn.argtypes = [_I, _I]
+    fn.restype = _I
+    return int(fn(num_heads, num_kv_heads))
+
+
+def diff_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
+                       positions: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor, out: torch.Tensor, num_heads: int,
+                       num_kv_heads: int, dim: int, vdim: int, window: int, scale: float, lam: float, eps: float, out_scale: float,
+                       segments: int = 0) -> torch.Tensor:
+    """``diff_attention`` on the tensor cores for bfloat16. ``tile_req``/``tile_tok0``: the work list (request and first
+    token of every tile of ``diff_mma_tokens_per_tile`` tokens). ``segments`` > 0: the keys are cut into that many segments
+    of ``DIFF_SEGMENT_KEYS`` with blocks of their own, and a second kernel adds them up (steps of few rows over many keys;
+    ``segments`` must cover the longest context)."""
+    N = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "diff_attention_mma takes bfloat16")
+    _need(q.stride(1) == 1 and q.shape[1] >= 2 * dim * num_heads and out.shape == (N, num_heads * vdim) and out.stride(1) == 1,
+          "differential attention shapes do not match")
+    _need(pages.is_contiguous() and pages.dim() == 4 and pages.shape[1] == num_kv_heads and pages.shape[3] == 2 * dim + vdim,
+          "differential attention pages have the wrong layout")
+    for t, name in ((tables, "tables"), (q_start, "q_start"), (ctx_len, "ctx_len"), (positions, "positions"), (tile_req, "tile_req"),
+                    (tile_tok0, "tile_tok0")):
+        _i32(t, name)
+    scratch = None
+    if segments > 0:
+        scratch = torch.empty(segments * N * num_heads * 2 * (vdim + 2), dtype=torch.float32, device=q.device)
+    _call("llmp_diff_attention_mma", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(pages), _ptr(tables), tables.shape[1],
+          _ptr(q_start), _ptr(ctx_len), _ptr(positions), _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), N, num_heads, num_kv_heads,
+          dim, vdim, pages.shape[2], int(window), float(scale), float(lam), float(eps), float(out_scale),
+          DIFF_SEGMENT_KEYS if segments > 0 else 0, int(segments), _ptr(scratch), _stream())
     return out

@@ -4,7 +4,7 @@ from .base import (Block, DepthMix, Embedding, FeedForward, Head, LayerCache, Mi
                    ResidualStream)
 from .registry import (kinds, lookup, register_block, register_depth_mix, register_embedding, register_feed_forward, register_head,
                        register_mixer, register_norm, register_position)
-from . import (attention, block, depth_mix, embedding, experts, feed_forward, latent_attention, norm, position,  # noqa: F401
+from . import (attention, block, depth_mix, differential_attention, embedding, experts, feed_forward, latent_attention, norm, position,  # noqa: F401
                recurrent)  # noqa: F401  (register the built-in kinds)
 
 __all__ = ["Block", "DepthMix", "Embedding", "FeedForward", "Head", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding",

@@ -56,11 +56,15 @@ class ResidualStream:
     addend is normed before it is added), and a mix over depth (``mix(weights, index)``: once the addend is in, the
     residual is this layer's result; it is kept as ``history[index]`` and replaced by ``sum_j weights[j] history[j]``,
     j = 0 .. index). ``history`` is float32 ``[results, tokens, hidden]`` with the embedding's output at 0; only models
-    with such a mix have one. The next norm kernel does all of it in one pass over the row."""
+    with such a mix have one. The next norm kernel does all of it in one pass over the row.
+
+    A block whose sublayers run side by side leaves two addends (``add``, then ``add_beside``); a norm that knows of it
+    (``layer_norm``) adds both in its kernel, everybody else sees their sum as the one pending addend."""
 
     def __init__(self, residual: torch.Tensor, history: Optional[torch.Tensor] = None):
         self.residual = residual
         self._pending = None
+        self._beside = None                           # a second addend, of a sublayer that ran beside the first
         self.pending_bias: Optional[torch.Tensor] = None
         self.pending_norm = None                      # a Norm part with ``weight`` and ``eps``: norms the addend
         self.pending_mix: Optional[Tuple[torch.Tensor, int]] = None
@@ -72,6 +76,26 @@ class ResidualStream:
         if self._pending is not None or self.pending_mix is not None:
             raise RuntimeError("the residual stream already holds a pending addend")
         self._pending, self.pending_bias, self.pending_norm = delta, bias, norm
+
+    def add_beside(self, delta: torch.Tensor) -> None:
+        """A second addend beside the pending one (the other sublayer of a block whose sublayers read the same input);
+        without bias or norm of its own."""
+        if self._pending is None or self._beside is not None or self.pending_norm is not None or self.pending_mix is not None:
+            raise RuntimeError("a second addend needs a plain first one and no other second one")
+        self._beside = delta.value() if isinstance(delta, PendingProduct) else delta
+
+    def take_addends(self):
+        """(first, second) pending addends as tensors, for a norm whose kernel adds both; only for a plain stream without a
+        pending bias. The caller clears them (``clear_addends``) once they are in the residual."""
+        return self.pending_raw(), self._beside
+
+    def pending_raw(self) -> Optional[torch.Tensor]:
+        if isinstance(self._pending, PendingProduct):
+            self._pending = self._pending.value()
+        return self._pending
+
+    def clear_addends(self) -> None:
+        self._pending, self._beside, self.pending_bias = None, None, None
 
     def mix(self, weights: torch.Tensor, index: int) -> None:
         """What the stream holds once the pending addend is in is result ``index``; what goes on is the weighted sum of
@@ -89,9 +113,11 @@ class ResidualStream:
 
     @property
     def pending(self) -> Optional[torch.Tensor]:
-        """The pending addend as a tensor (a product not yet taken is taken now)."""
+        """The pending addend as a tensor (a product not yet taken is taken now; two addends become their float32 sum)."""
         if isinstance(self._pending, PendingProduct):
             self._pending = self._pending.value()
+        if self._beside is not None:
+            self._pending, self._beside = self._pending.float() + self._beside.float(), None
         return self._pending
 
     @pending.setter
@@ -135,7 +161,7 @@ class ResidualStream:
     def take_pending_product(self) -> Optional[PendingProduct]:
         """The pending addend if it is a product not yet taken and without bias, which is then the caller's to add;
         else None, and nothing changes."""
-        if isinstance(self._pending, PendingProduct) and self.pending_bias is None and self.plain:
+        if isinstance(self._pending, PendingProduct) and self.pending_bias is None and self.plain and self._beside is None:
             product, self._pending = self._pending, None
             return product
         return None

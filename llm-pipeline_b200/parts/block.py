@@ -56,3 +56,22 @@ class SandwichNormResidualBlock(Block):
             stream.add(out, bias, norm=self.norms["feed_forward_out"])
         if self.depth_mix is not None:
             stream.mix(self.depth_mix.weights, self.depth_mix.index)
+
+
+@register_block("parallel_residual")
+class ParallelResidualBlock(Block):
+    """One norm, and both sublayers read its output: ``x += mixer(norm(x)) + feed_forward(norm(x))`` (a layer without a
+    feed-forward adds the mixer's output alone). Neither sum is taken here: the two outputs are left pending on the
+    stream side by side, and the next norm kernel adds both into the float32 residual before it norms the row."""
+
+    NORMS = ("mixer",)
+
+    def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
+        h = self.norms["mixer"].add_norm(stream, ctx)
+        out, bias = self.mixer.forward(h, ctx, cache)
+        stream.add(out, bias)
+        if self.feed_forward is not None:
+            out, bias = self.feed_forward.forward(h, ctx)
+            if bias is not None:
+                out = out.float() + bias.float()
+            stream.add_beside(out)

@@ -19,9 +19,10 @@ from .registry import register_embedding, register_head
 class TokenEmbedding(Embedding):
     graph_safe = True
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, name: Optional[str] = None):
-        """``name``: the table's full tensor name where it is not ``<prefix>.weight``."""
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, name: Optional[str] = None, scale: float = 1.0):
+        """``name``: the table's full tensor name where it is not ``<prefix>.weight``; ``scale``: a factor on every row."""
         self.prefix, self.vocab_size, self.hidden_size = prefix, int(vocab_size), int(hidden_size)
+        self.scale = float(scale)
         self.name = name or f"{prefix}.weight"
         self.weight: Optional[torch.Tensor] = None
 
@@ -33,7 +34,7 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ctx) -> torch.Tensor:
         out = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=ctx.device)
-        kernels.embedding(ctx.token_ids, self.weight, out)
+        kernels.embedding(ctx.token_ids, self.weight, out, self.scale)
         return out
 
 
@@ -68,9 +69,11 @@ class LinearHead(Head):
     graph_safe = True
 
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
-                 tied_name: Optional[str] = None, softcap: Optional[float] = None):
+                 tied_name: Optional[str] = None, softcap: Optional[float] = None, name: Optional[str] = None):
         """``tied_to``: the prefix of the embedding whose table the head uses (``tied_name``: that table's full tensor
-        name where it is not ``<tied_to>.weight``). ``softcap``: logits become ``cap * tanh(logits / cap)``."""
+        name where it is not ``<tied_to>.weight``). ``softcap``: logits become ``cap * tanh(logits / cap)``. ``name``: the
+        full name of an untied head's matrix where it is not ``<prefix>.weight``."""
+        self.name = name or f"{prefix}.weight"
         self.prefix, self.vocab_size, self.hidden_size, self.tied_to = prefix, int(vocab_size), int(hidden_size), tied_to
         self.tied_name = tied_name or (f"{tied_to}.weight" if tied_to else None)
         self.softcap = float(softcap) if softcap else None
@@ -78,15 +81,15 @@ class LinearHead(Head):
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         # A tied head has no tensor of its own; a checkpoint may still carry a copy, which must be one.
-        return {f"{self.prefix}.weight": ParamSpec((self.vocab_size, self.hidden_size), optional=self.tied_to is not None)}
+        return {self.name: ParamSpec((self.vocab_size, self.hidden_size), optional=self.tied_to is not None)}
 
     def copies(self) -> Dict[str, str]:
         # The reference makes the head's parameter the embedding's own tensor when tie_word_embeddings is set
         # (models/qwen3/custom_builder.py:389-391), so a checkpoint it wrote holds the same values under both names.
-        return {f"{self.prefix}.weight": self.tied_name} if self.tied_to else {}
+        return {self.name: self.tied_name} if self.tied_to else {}
 
     def load(self, get: TensorGetter) -> None:
-        self.weight = get(self.tied_name if self.tied_to else f"{self.prefix}.weight", "matrix")
+        self.weight = get(self.tied_name if self.tied_to else self.name, "matrix")
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         logits = linear(x, self.weight, out_dtype=torch.float32)

@@ -1,4 +1,4 @@
-"""RMSNorm fused with the residual add.
+"""Norms fused with the residual add: RMSNorm, and layer norm with weight and bias.
 
 Formula of src/llm_pipeline/models/qwen3/custom_builder.py:53-58: in float32,
 ``weight * (x * rsqrt(mean(x^2) + eps))``, rounded once to the compute type. The residual adds of
@@ -68,3 +68,44 @@ class RMSNorm(Norm):
             return kernels.add_rmsnorm(residual, None, self.weight, self.eps, out)
 
         return residual_product(product, residual, self.weight, self.eps, finished)
+
+
+@register_norm("layer_norm")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w + b`` with var the mean of the squared deviations, in float32, rounded once to
+    the compute type. The kernel first adds what is pending on the stream into the float32 residual: one addend, or the
+    two of a block whose sublayers ran side by side. ``name`` / ``bias_name``: the tensors' full names where they are not
+    ``<prefix>.weight`` / ``<prefix>.bias``."""
+
+    graph_safe = True
+
+    def __init__(self, prefix: str, size: int, eps: float, name: Optional[str] = None, bias_name: Optional[str] = None):
+        self.prefix, self.size, self.eps = prefix, int(size), float(eps)
+        self.name = name or f"{prefix}.weight"
+        self.bias_name = bias_name or f"{prefix}.bias"
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.name: ParamSpec((self.size,), role="vector", init="norm"),
+                self.bias_name: ParamSpec((self.size,), role="vector", init="small")}
+
+    def load(self, get: TensorGetter) -> None:
+        self.weight = get(self.name, "vector").contiguous()
+        self.bias = get(self.bias_name, "vector").contiguous()
+        if self.weight.dtype != self.bias.dtype:
+            self.weight, self.bias = self.weight.float(), self.bias.float()
+
+    def add_norm(self, stream: ResidualStream, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        count = rows.numel() if rows is not None else stream.residual.shape[0]
+        out = torch.empty((count, self.size), dtype=ctx.dtype, device=stream.residual.device)
+        if not stream.plain:
+            stream.fold()                               # a normed addend or a mix over depth: the general kernel first
+        first, second = stream.take_addends()
+        if first is not None and stream.pending_bias is not None:
+            first, second = stream.pending, None        # a bias on the addend: summed by the stream
+            first = first.float() + stream.pending_bias.float()
+        kernels.add_layernorm(stream.residual, first, second, self.weight, self.bias, self.eps, out, rows=rows)
+        if rows is None:
+            stream.clear_addends()
+        return out

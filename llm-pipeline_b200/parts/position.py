@@ -5,9 +5,17 @@ src/llm_pipeline/models/qwen3/custom_builder.py:269-288: ``inv_freq[j] = 1 / the
 (1.0), all in float32. The tables are ``[tokens, rotary_dim / 2]`` because the reference's
 ``cat(freqs, freqs)`` repeats them; the mixer's kernel pairs entry j with j + rotary_dim/2
 (custom_builder.py:85-99). The reference rounds the tables to the activations' type
-(custom_builder.py:288); here they stay float32."""
+(custom_builder.py:288); here they stay float32.
+
+``frequency_scaling`` (optional: ``factor``, ``low``, ``high``, ``original``) rescales the frequencies by wavelength
+before any angle is taken: with wavelength l = 2 pi / f, f stays where l < original / high, becomes f / factor where
+l > original / low, and between the two is the blend (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+The frequencies are computed in float64 on the host and stored as float32; angles are float32 products."""
 
 from __future__ import annotations
+
+import math
+from typing import Dict, Optional
 
 import torch
 
@@ -20,13 +28,37 @@ from .registry import register_position
 class RotaryPositions(PositionEncoding):
     graph_safe = True
 
-    def __init__(self, prefix: str, rotary_dim: int, theta: float, scaling: float = 1.0):
+    def __init__(self, prefix: str, rotary_dim: int, theta: float, scaling: float = 1.0,
+                 frequency_scaling: Optional[Dict[str, float]] = None):
         if rotary_dim <= 0 or rotary_dim % 2:
             raise ValueError(f"rotary_dim must be positive and even, got {rotary_dim}")
         self.prefix, self.rotary_dim, self.theta, self.scaling = prefix, int(rotary_dim), float(theta), float(scaling)
-        exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).float() / self.rotary_dim
-        self._inv_freq_cpu = 1.0 / (self.theta ** exponent)
+        self.frequency_scaling = dict(frequency_scaling) if frequency_scaling else None
+        if self.frequency_scaling is None:
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).float() / self.rotary_dim
+            self._inv_freq_cpu = 1.0 / (self.theta ** exponent)
+        else:
+            self._inv_freq_cpu = torch.tensor(self.rescaled_frequencies(self.rotary_dim, self.theta, self.frequency_scaling),
+                                              dtype=torch.float64).float()
         self._inv_freq = None
+
+    @staticmethod
+    def rescaled_frequencies(rotary_dim: int, theta: float, rule: Dict[str, float]):
+        factor, low, high, original = (float(rule[k]) for k in ("factor", "low", "high", "original"))
+        if not (factor > 0 and high > low and original > 0):
+            raise ValueError(f"frequency scaling needs factor > 0, high > low and original > 0, got {rule}")
+        out = []
+        for j in range(rotary_dim // 2):
+            f = theta ** (-2.0 * j / rotary_dim)
+            wave = 2.0 * math.pi / f
+            if wave < original / high:
+                out.append(f)
+            elif wave > original / low:
+                out.append(f / factor)
+            else:
+                s = (original / wave - low) / (high - low)
+                out.append((1.0 - s) * f / factor + s * f)
+        return out
 
     def tables(self, ctx):
         if self._inv_freq is None or self._inv_freq.device != ctx.device:
