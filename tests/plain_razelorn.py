@@ -60,6 +60,29 @@ def rotate_half(v: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor) ->
     return torch.cat([a * cos - b * sin, b * cos + a * sin, v[..., 2 * half:]], dim=-1)
 
 
+def two_map_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor, window: Optional[int],
+                      scale: float, lam: float, diff: float, eps: float) -> torch.Tensor:
+    """q [n, H, 2, d], k [n, G, 2, d], v [n, G, dv] as they enter the scores (normed and rotated) -> [n, H dv]: per head
+    two softmax maps over the visible keys, a1 - lam a2, divided by its root mean square, times 1 - diff."""
+    n, H, G = q.shape[0], q.shape[1], k.shape[1]
+    i, j = positions[:, None], positions[None, :]
+    visible = (j <= i) if window is None else ((j <= i) & (i - j < int(window)))
+    heads = []
+    for head in range(H):
+        g = head // (H // G)
+        maps = []
+        for which in range(2):
+            score = (q[:, head, which] @ k[:, g, which].T) * scale
+            score = score.masked_fill(~visible, float("-inf"))
+            maps.append(torch.softmax(score, dim=-1) @ v[:, g])
+        heads.append(rms(maps[0] - lam * maps[1], eps) * (1.0 - diff))
+    return torch.cat(heads, dim=-1)
+
+
+def map_factor(W: Dict[str, torch.Tensor], p: str, diff: float) -> torch.Tensor:
+    return torch.exp((W[f"{p}.lq1"] * W[f"{p}.lk1"]).sum()) - torch.exp((W[f"{p}.lq2"] * W[f"{p}.lk2"]).sum()) + diff
+
+
 def differential_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float,
                            positions: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Two softmax maps per head over the same values; the second is subtracted with a learned factor, the difference
@@ -77,22 +100,9 @@ def differential_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, 
     if rot and int(rot.get("dims", 0)) > 0:
         freq = rotary_frequencies(int(rot["dims"]), float(rot["base"]), rot.get("scaling"), h.dtype)
         q, k = rotate_half(q, positions, freq), rotate_half(k, positions, freq)
-    lam = (torch.exp((W[f"{p}.lq1"] * W[f"{p}.lk1"]).sum()) - torch.exp((W[f"{p}.lq2"] * W[f"{p}.lk2"]).sum()) + diff)
     window = (m.get("mask") or {}).get("size")
-    i = positions[:, None]
-    j = positions[None, :]
-    visible = (j <= i) if window is None else ((j <= i) & (i - j < int(window)))
-    heads = []
-    for head in range(H):
-        g = head // (H // G)
-        maps = []
-        for which in range(2):
-            score = (q[:, head, which] @ k[:, g, which].T) * float(m["scale"])
-            score = score.masked_fill(~visible, float("-inf"))
-            maps.append(torch.softmax(score, dim=-1) @ v[:, g])
-        o = maps[0] - lam * maps[1]
-        heads.append(rms(o, eps) * (1.0 - diff))
-    return torch.cat(heads, dim=-1) @ W[f"{p}.o"].T
+    heads = two_map_attention(q, k, v, positions, window, float(m["scale"]), float(map_factor(W, p, diff)), diff, eps)
+    return heads @ W[f"{p}.o"].T
 
 
 def dense_ff(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
