@@ -27,6 +27,9 @@ latent-attention mixers, dense and routed-expert feed-forwards) at real layer si
 same width, depth and vocabulary: a 2,048-token prompt, decode at ``--batch`` requests of 2,048 tokens, and the device
 time of every kernel class of both, in one JSON line of its own shape.
 
+``--compare razelorn [--size 1k|2k]`` does the same for the Razelorn decoder (differential attention under a sliding
+window beside a dense or routed-expert feed-forward on one layer norm).
+
 ``--impl reference`` runs DavidAkinpelu/llm-pipeline's own ``Qwen3ForCausalLM`` from
 ``baseline/_ref`` (installed offline with pip --no-deps --target) with its ``past_key_values``
 loop at the same sizes and prints the same line with ``"impl": "reference"``.
@@ -743,16 +746,71 @@ def compare_one(cfg_json, work_of, peak, args, label=None):
     return out
 
 
+# ``--compare razelorn``: the same two measurements for the Razelorn decoder: four layers (differential attention under a
+# sliding window beside a squared-ReLU feed-forward, then beside routed experts with identity experts and a shared expert,
+# then that layer's tensors once more, then a layer of its own again) beside a Qwen3 dense decoder of the same width, depth
+# and vocabulary whose heads hold as many query and key entries.
+RAZELORN_SIZES = {
+    "1k": {"width": 1024, "heads": 8, "kv_heads": 2, "dim": 64, "vdim": 128, "window": 2048, "rot": 32, "ff": 4096,
+           "experts": 16, "top": 2, "identity": 2, "expert_ff": 1024, "shared_ff": 1024, "layers": 4, "vocab": 32000, "qwen_heads": (8, 4)},
+    "2k": {"width": 2048, "heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "window": 2048, "rot": 64, "ff": 8192,
+           "experts": 32, "top": 4, "identity": 2, "expert_ff": 1408, "shared_ff": 2048, "layers": 4, "vocab": 32000, "qwen_heads": (16, 8)},
+}
+
+
+def razelorn_config(z):
+    mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "diff": 0.5,
+             "mask": {"size": z["window"]},
+             "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"], "identity": z["identity"]},
+           "shared": {"ff": z["shared_ff"]}}
+    layers = [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": z["ff"]}},
+              {"type": "attention", "mixer": mixer, "mlp": moe}]
+    while len(layers) < z["layers"]:
+        own = len(layers) % 2 == 1
+        layers.append({"type": "attention", "mixer": mixer, "mlp": moe, **({} if own else {"weights_of": 1})})
+    return {"architecture": "Razelorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": layers}
+
+
+def razelorn_work(z, tokens, keys_per_token, decode):
+    """Closed-form work of the design's own kernel classes for one step: label -> (bytes, flops)."""
+    D, L = z["width"], z["layers"]
+    H, G, d, dv = z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    moe_layers, dense_layers = L - 1, 1
+    keys = min(keys_per_token, z["window"])
+    work = {}
+    # per layer: residual read and written, two float32 addends read, the normed row written; the head's rows beside
+    work["add_layernorm"] = (tokens * D * L * (4 + 4 + 4 + 4 + 2), 0.0)
+    work["diff_qkv_post"] = (L * tokens * (2 * d * (H + G) + G * dv) * (2 + 2), 0.0)
+    work["relu_squared"] = (dense_layers * tokens * z["ff"] * 4, 0.0)
+    work["swiglu"] = (moe_layers * tokens * z["shared_ff"] * 6, 0.0)
+    if decode:
+        work["diff_attention_mma"] = (L * tokens * keys * G * (2 * d + dv) * 2, 0.0)
+    else:
+        work["diff_attention_mma"] = (0.0, L * 2.0 * tokens * keys * H * (2 * d + 2 * dv))
+    pairs = tokens * z["top"] * z["experts"] / (z["experts"] + z["identity"])      # pairs that name an expert with matrices
+    expert_weights = 3 * z["expert_ff"] * D * 2
+    if decode:
+        work["expert_rows"] = (moe_layers * pairs * expert_weights, 0.0)
+    else:
+        work["expert_rows"] = (0.0, moe_layers * 2.0 * pairs * 3 * z["expert_ff"] * D)
+    work["expert_grouped"] = work["expert_rows"]
+    return work
+
+
 def run_compare(args):
     peak = peaks()
-    z = ZUPILORN_SIZES[args.size]
+    sizes, config_of, work_of = {"zupilorn": (ZUPILORN_SIZES, zupilorn_config, zupilorn_work),
+                                 "razelorn": (RAZELORN_SIZES, razelorn_config, razelorn_work)}[args.compare]
+    z = sizes[args.size]
     clocks = ClockSampler()
     clocks.start()
-    ours = compare_one(zupilorn_config(z), lambda n, k, d: zupilorn_work(z, n, k, d), peak, args)
+    ours = compare_one(config_of(z), lambda n, k, d: work_of(z, n, k, d), peak, args)
     qcfg = qwen_config_like(z)
     beside = compare_one(qcfg, lambda n, k, d: qwen_work(qcfg, n, k, d), peak, args, product_labels(qcfg))
-    print(json.dumps({"compare": "zupilorn", "size": args.size, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
-                      "sizes": z, "zupilorn": ours, "qwen3_same_width_and_depth": beside, "peaks": peak, "clocks": clocks.stop()}))
+    print(json.dumps({"compare": args.compare, "size": args.size, "dtype": "bf16", "data": "synthetic (seeded random weights and token ids)",
+                      "sizes": z, args.compare: ours, "qwen3_same_width_and_depth": beside, "peaks": peak, "clocks": clocks.stop()}))
     return 0
 
 
@@ -840,7 +898,7 @@ def main() -> int:
     parser.add_argument("--lean", action="store_true", help="leave out the per-kernel breakdown, the page-size point, the plain "
                         "PyTorch baseline and the self-check")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
-    parser.add_argument("--compare", default="", choices=("", "zupilorn"),
+    parser.add_argument("--compare", default="", choices=("", "zupilorn", "razelorn"),
                         help="instead of the headline: prefill and decode of this design at real layer sizes beside a Qwen3 dense "
                         "decoder of the same width and depth, with the time of every kernel class")
     parser.add_argument("--size", default="2k", choices=tuple(ZUPILORN_SIZES), help="with --compare: the layer sizes")
