@@ -96,9 +96,8 @@ class RazelornConfig(ModelConfig):
                 if not 0 <= int(j) < len(self.layers) or int(j) == i or self.layers[int(j)].get("weights_of") is not None:
                     problems.append(f"layer {i}: weights_of must name another layer that has tensors of its own, got {j}")
                     continue
-                other = self.layers[int(j)]
-                if (other.get("type"), other.get("mixer"), other.get("mlp")) != (kind, layer.get("mixer"), mlp):
-                    problems.append(f"layer {i} uses the tensors of layer {j} but describes another layer")
+                # the layer runs layer j's parts, so layer j's description is the one that counts
+                kind, mixer, mlp = self.layers[int(j)].get("type"), self.layers[int(j)].get("mixer") or {}, self.layers[int(j)].get("mlp")
             lacking = [k for k in ("heads", "kv_heads", "dim", "vdim", "scale", "diff") if mixer.get(k) is None]
             if lacking:
                 problems.append(f"layer {i}: the attention mixer lacks {lacking}")

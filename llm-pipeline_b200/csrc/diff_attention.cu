@@ -16,66 +16,109 @@
 
 #define DA_KEYS 32
 #define DA_WARPS 8
-#define DA_POST_WARPS 4
+#define DA_POST_THREADS 256
 #define DA_MAX_D 256
 
-template <typename T>
-__global__ void __launch_bounds__(DA_POST_WARPS * 32)
+// One block per token. The whole row [q | k | v] goes to shared memory in one sweep of 16-byte loads (all in flight at
+// once). Norm weight and rotation are folded into two coefficient vectors per token, for q and for k:
+// out[i] = rstd (x[i] A[i] + x[partner(i)] B[i]) with A = w cos, B = -/+ w[partner] sin inside the rotated part and
+// A = w, B = 0 outside it. Then a warp owns a run of d entries at a time: sum of squares, the two products per entry, and
+// the store to the run's place (q back into the row, k into the token's cache rows), two entries a lane where the sizes
+// are even. v is copied to the cache rows as it is.
+template <typename T> struct PostPair;
+template <> struct PostPair<float> { typedef float2 type; static __device__ __forceinline__ float2 make(float a, float b) { return make_float2(a, b); } };
+template <> struct PostPair<bf16> { typedef __nv_bfloat162 type; static __device__ __forceinline__ __nv_bfloat162 make(float a, float b) { return __floats2bfloat162_rn(a, b); } };
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(DA_POST_THREADS)
 diff_qkv_post_kernel(T* __restrict__ qkv, long ld, int H, int G, int d, int dv, const void* __restrict__ qw, const void* __restrict__ kw,
                      int w_bf16, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
                      const int* __restrict__ slots, T* __restrict__ pages, int page_size) {
-    __shared__ float unit[DA_POST_WARPS][DA_MAX_D];
-    const int n = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    T* row = qkv + (size_t)n * ld;
+    extern __shared__ __align__(16) unsigned char post_raw[];
+    const int units = 2 * H + 2 * G, q_units = 2 * H;
+    const int qk = units * d, width = qk + G * dv;
     const int half = rot / 2;
-    const float* cs = cos_t + (size_t)n * half;
-    const float* sn = sin_t + (size_t)n * half;
+    float* coef = reinterpret_cast<float*>(post_raw);        // [2][2][d]: A and B for q, then for k
+    T* vals = reinterpret_cast<T*>(post_raw + (((size_t)(4 * d) * sizeof(float) + 15) / 16) * 16);   // [width]: the row as stored
+    const int n = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    pdl_wait();
+    pdl_trigger();
+    T* row = qkv + (size_t)n * ld;
+    for (int e = threadIdx.x; e < 2 * d; e += blockDim.x) {
+        const int which = e >= d, i = which ? e - d : e;
+        const void* w = which ? kw : qw;
+        float a = load_as_float(w, w_bf16, i), b = 0.f;
+        if (i < half) {
+            const float c = cos_t[(size_t)n * half + i], sv = sin_t[(size_t)n * half + i];
+            b = -load_as_float(w, w_bf16, i + half) * sv;
+            a *= c;
+        } else if (i < rot) {
+            const float c = cos_t[(size_t)n * half + i - half], sv = sin_t[(size_t)n * half + i - half];
+            b = load_as_float(w, w_bf16, i - half) * sv;
+            a *= c;
+        }
+        coef[which * 2 * d + i] = a;
+        coef[which * 2 * d + d + i] = b;
+    }
     const int slot = slots ? slots[n] : -1;
     const int rs = 2 * d + dv;
     T* page_row = nullptr;                                   // the token's row of key/value head 0
     if (pages && slot >= 0)
         page_row = pages + (((size_t)(slot / page_size) * G) * page_size + slot % page_size) * rs;
     const size_t head_step = (size_t)page_size * rs;         // from one key/value head's row to the next one's
-    const int q_units = 2 * H, units = 2 * H + 2 * G;
-    float* mine = unit[warp];
-    for (int u = warp; u < units; u += DA_POST_WARPS) {
+    const int live = page_row ? width : q_units * d;         // without a cache row keys and values are not needed
+    if (VEC) {
+        constexpr int PER = 16 / sizeof(T);
+        const uint4* src = reinterpret_cast<const uint4*>(row);
+        uint4* dst = reinterpret_cast<uint4*>(vals);
+        for (int e = threadIdx.x; e < live / PER; e += blockDim.x) dst[e] = src[e];
+    } else {
+        for (int e = threadIdx.x; e < live; e += blockDim.x) vals[e] = row[e];
+    }
+    __syncthreads();
+    if (page_row) {                                          // the values pass as they are
+        const T* v = vals + qk;
+        if (VEC) {
+            constexpr int PER = 16 / sizeof(T);
+            const int per_head = dv / PER;
+            for (int e = threadIdx.x; e < G * per_head; e += blockDim.x) {
+                const int g = e / per_head, c = e - g * per_head;
+                reinterpret_cast<uint4*>(page_row + (size_t)g * head_step + 2 * d)[c] = reinterpret_cast<const uint4*>(v + (size_t)g * dv)[c];
+            }
+        } else {
+            for (int e = threadIdx.x; e < G * dv; e += blockDim.x) {
+                const int g = e / dv, c = e - g * dv;
+                page_row[(size_t)g * head_step + 2 * d + c] = v[e];
+            }
+        }
+    }
+    const int live_units = page_row ? units : q_units;
+    for (int u = warp; u < live_units; u += nwarps) {
+        const T* x = vals + u * d;
         const bool is_key = u >= q_units;
-        if (is_key && !page_row) continue;
-        T* src = row + (size_t)u * d;
+        const float* A = coef + (is_key ? 2 * d : 0);
+        const float* B = A + d;
         float ss = 0.f;
         for (int i = lane; i < d; i += 32) {
-            const float v = to_float(src[i]);
-            mine[i] = v;
-            ss += v * v;
+            const float v = to_float(x[i]);
+            ss = fmaf(v, v, ss);
         }
-        ss = warp_sum(ss);
-        const float rstd = rsqrtf(ss / (float)d + eps);
-        const void* w = is_key ? kw : qw;
-        __syncwarp();
-        T* dst = src;
+        const float r = rsqrtf(warp_sum(ss) / (float)d + eps);
+        T* dst = row + (size_t)u * d;
         if (is_key) {
             const int ku = u - q_units;                      // key/value head ku / 2, map ku % 2
             dst = page_row + (size_t)(ku >> 1) * head_step + (size_t)(ku & 1) * d;
         }
-        for (int i = lane; i < d; i += 32) {
-            float v = mine[i] * rstd * load_as_float(w, w_bf16, i);
-            if (i < half) {
-                const float o = mine[i + half] * rstd * load_as_float(w, w_bf16, i + half);
-                v = v * cs[i] - o * sn[i];
-            } else if (i < rot) {
-                const float o = mine[i - half] * rstd * load_as_float(w, w_bf16, i - half);
-                v = v * cs[i - half] + o * sn[i - half];
-            }
-            dst[i] = from_float<T>(v);
-        }
-        __syncwarp();
-    }
-    if (page_row) {
-        const T* v = row + (size_t)units * d;
-        for (int e = threadIdx.x; e < G * dv; e += blockDim.x) {
-            const int g = e / dv, c = e % dv;
-            page_row[(size_t)g * head_step + 2 * d + c] = v[e];
+        auto entry = [&](int i) {
+            const int partner = i < half ? i + half : (i < rot ? i - half : i);
+            return r * fmaf(to_float(x[i]), A[i], to_float(x[partner]) * B[i]);
+        };
+        if (VEC) {                                           // d is even and every run starts on a 4-byte boundary
+            for (int i = 2 * lane; i < d; i += 64)
+                *reinterpret_cast<typename PostPair<T>::type*>(dst + i) = PostPair<T>::make(entry(i), entry(i + 1));
+        } else {
+            for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(entry(i));
         }
     }
 }
@@ -88,14 +131,27 @@ LLMP_API int llmp_diff_qkv_post(void* qkv, int dtype, long ld, int H, int G, int
                  "diff_qkv_post: bad sizes heads=%d kv_heads=%d dim=%d vdim=%d rotated=%d", H, G, d, dv, rot);
     LLMP_REQUIRE(rot == 0 || (cos_t && sin_t), "diff_qkv_post: a rotation needs its tables");
     LLMP_REQUIRE(!pages || (slots && page_size > 0), "diff_qkv_post: pages need slots and a page size");
-    if (dtype == LLMP_F32)
-        diff_qkv_post_kernel<float><<<N, DA_POST_WARPS * 32, 0, stream>>>((float*)qkv, ld, H, G, d, dv, q_weight, k_weight,
-                                                                          w_dtype == LLMP_BF16, eps, cos_t, sin_t, rot, slots,
-                                                                          (float*)pages, page_size);
-    else
-        diff_qkv_post_kernel<bf16><<<N, DA_POST_WARPS * 32, 0, stream>>>((bf16*)qkv, ld, H, G, d, dv, q_weight, k_weight,
-                                                                         w_dtype == LLMP_BF16, eps, cos_t, sin_t, rot, slots,
-                                                                         (bf16*)pages, page_size);
+    const size_t elem = dtype == LLMP_F32 ? 4 : 2;
+    const size_t width = (size_t)(2 * H + 2 * G) * d + (size_t)G * dv;
+    const size_t smem = (((size_t)(4 * d) * sizeof(float) + 15) / 16) * 16 + width * elem + 16;
+    LLMP_REQUIRE(smem <= 200 * 1024, "diff_qkv_post: %d heads of %d entries do not fit shared memory", H, d);
+    // 16-byte pieces and pairs of entries: every run, row and cache row must start on such a boundary
+    const int per = (int)(16 / elem);
+    const bool vec = d % per == 0 && dv % per == 0 && ld % per == 0 && ((size_t)qkv % 16) == 0 && ((size_t)pages % 16) == 0;
+    cudaError_t e;
+#define LLMP_POST(T, V)                                                                                                              \
+    do {                                                                                                                             \
+        LLMP_ALLOW_SMEM((diff_qkv_post_kernel<T, V>), smem);                                                                         \
+        e = llmp_launch_dependent(diff_qkv_post_kernel<T, V>, dim3(N), dim3(DA_POST_THREADS), smem, stream, (T*)qkv, ld, H, G, d, dv, \
+                                  q_weight, k_weight, (int)(w_dtype == LLMP_BF16), eps, cos_t, sin_t, rot, slots, (T*)pages, page_size); \
+    } while (0)
+    if (dtype == LLMP_F32) {
+        if (vec) LLMP_POST(float, true); else LLMP_POST(float, false);
+    } else {
+        if (vec) LLMP_POST(bf16, true); else LLMP_POST(bf16, false);
+    }
+#undef LLMP_POST
+    LLMP_REQUIRE(e == cudaSuccess, "diff_qkv_post: %s", cudaGetErrorString(e));
     return llmp_check_launch("diff_qkv_post");
 }
 

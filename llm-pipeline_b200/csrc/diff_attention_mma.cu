@@ -10,9 +10,15 @@
 // the causal diagonal or below the window are skipped. At the end a row's two outputs are combined in registers:
 // a1 - lambda a2, divided by its root mean square over the dv entries (a sum over the row's quad of lanes), scaled.
 //
+// The key/value tile has two buffers where two blocks of that size still fit an SM: the copy of the next tile runs under
+// the products of this one.
+//
 // Steps of few rows over many keys (decoding): `segments` > 0 cuts the keys into segments of `segment_keys` (a multiple
 // of the tile), every segment with blocks of its own that leave both maps' sums (maximum, sum, output; float32) in
-// scratch; a second kernel adds a row's segments in their order and does the combination.
+// scratch and count themselves; the block of a tile that counts last adds the rows' segments in their order and does the
+// combination (nobody waits, no second kernel; the counters are left at zero). When every tile is one token
+// (`split`), its rows fit one warp's 16, and the four warps share a key tile instead: warp w takes half w / 2 of the
+// tile's keys for map w % 2 and leaves sums of its own, so a segment has two sets of sums per map.
 #include "common.cuh"
 
 #define DM_ROWS 64
@@ -28,12 +34,14 @@ struct DiffMmaParams {
     const int* ctx_len;
     const int* tile_req;
     const int* tile_tok0;
-    float* scratch;                  // segments: [segment][token][head][2 (dv + 2)]
+    int* counters;                   // segments: one per (tile, kv head, chunk of heads), zero before and after a launch
+    const int* positions;
+    float* scratch;                  // segments: [segment][half of the tiles' keys, if split][token][head][map][dv + 2]
     long q_stride, out_stride;
     int table_stride;
     int nq, nkv, page_size, window;
     int heads_per_cta, tokens_per_cta, head_chunks, num_tiles;
-    int segment_keys, segments, total_tokens;
+    int segment_keys, segments, total_tokens, split, stages;
     float scale, lambda, eps, out_scale;
 };
 
@@ -73,6 +81,60 @@ __device__ __forceinline__ unsigned dm_pack(float lo, float hi) {
     return *reinterpret_cast<const unsigned*>(&v);
 }
 
+// One warp adds the sums that the segments left for row (token n, head h) at position `pos`, both maps, in the order of the
+// segments' keys, and combines them: a1 - lambda a2, its norm, the store. The row's segments are those that hold a key it
+// sees: from the one with its window's first key to the one with its own. Read past L1: other blocks wrote them.
+__device__ __forceinline__ void dm_merge_row(const DiffMmaParams& p, int n, int h, int pos, int dv, int lane) {
+    const int sets = p.split ? 2 : 1;
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int s_lo = lo / p.segment_keys, s_hi = pos / p.segment_keys;
+    const int w = 2 * (dv + 2);
+    const int first = s_lo * sets, count = (s_hi + 1) * sets - first;
+    const float* base = p.scratch + (((size_t)first * p.total_tokens + n) * p.nq + h) * w;
+    const size_t step = (size_t)p.total_tokens * p.nq * w;       // from one set of sums to the next
+    // the maxima first (a lane per set), so that the sets can then be added without waiting for one another
+    float m_all[2] = {-INFINITY, -INFINITY};
+    for (int s = lane; s < count; s += 32) {
+        m_all[0] = fmaxf(m_all[0], __ldcg(base + s * step));
+        m_all[1] = fmaxf(m_all[1], __ldcg(base + s * step + dv + 2));
+    }
+    m_all[0] = warp_max(m_all[0]);
+    m_all[1] = warp_max(m_all[1]);
+    float acc[2][4], l_all[2] = {0.f, 0.f};
+#pragma unroll
+    for (int m = 0; m < 2; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < count; ++s) {                            // in the order of the sets' keys
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            const float* s2 = base + s * step + m * (dv + 2);
+            const float a = exp2f(__ldcg(s2) - m_all[m]);        // log2 units, as the blocks keep them; 0 for a set without a visible key
+            l_all[m] = fmaf(__ldcg(s2 + 1), a, l_all[m]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c = lane + 32 * i;
+                if (c < dv) acc[m][i] = fmaf(__ldcg(s2 + 2 + c), a, acc[m][i]);
+            }
+        }
+    }
+    const float i1 = 1.f / l_all[0], i2 = p.lambda / l_all[1];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = lane + 32 * i;
+        acc[0][i] = c < dv ? acc[0][i] * i1 - acc[1][i] * i2 : 0.f;
+        ss = fmaf(acc[0][i], acc[0][i], ss);
+    }
+    ss = warp_sum(ss);
+    const float rn = rsqrtf(ss / (float)dv + p.eps) * p.out_scale;
+    bf16* dst = p.out + (size_t)n * p.out_stride + (size_t)h * dv;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = lane + 32 * i;
+        if (c < dv) dst[c] = __float2bfloat16_rn(acc[0][i] * rn);
+    }
+}
+
 // D16: key size / 16; V16: value size / 16. With p.segments > 0 the keys are cut into segments (blockIdx.y) whose sums go
 // to scratch.
 template <int D16, int V16>
@@ -83,11 +145,14 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
     constexpr int QW = 2 * D, RS = 2 * D + DV;                   // a query row (both maps), a cached row
     constexpr int QSTRIDE = QW + 8, KSTRIDE = RS + 8;            // padded rows: conflict-free ldmatrix
     bf16* Qs = reinterpret_cast<bf16*>(dm_smem);                 // [DM_ROWS][QSTRIDE]
-    bf16* KVs = Qs + DM_ROWS * QSTRIDE;                          // [DM_KEYS][KSTRIDE]
-    __shared__ long long key_off[DM_KEYS];
+    bf16* ring = Qs + DM_ROWS * QSTRIDE;                         // [stages][DM_KEYS][KSTRIDE]
+    constexpr int STAGE_ELEMS = DM_KEYS * KSTRIDE;
+    __shared__ long long key_off[2][DM_KEYS];
+    const bool split = p.split != 0;                             // four warps on the 16 rows of a one-token tile
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int rw = split ? 0 : warp;                             // which 16 rows of the tile this warp works on
     const int per_tile = p.nkv * p.head_chunks;
     const int tile = p.num_tiles - 1 - (int)(blockIdx.x / (unsigned)per_tile);      // long tiles first
     const int in_tile = (int)(blockIdx.x % (unsigned)per_tile);
@@ -115,6 +180,7 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
         if (lo < 0) lo = 0;
     }
     int tile_lo = (lo / DM_KEYS) * DM_KEYS;
+    const int hi_tile = hi;                                      // the tile's last key, before a segment clips it
     if (SEG) {
         // segment s of a row holds the keys [s * segment_keys, (s + 1) * segment_keys) of its request, whatever the step
         const int s0 = (int)blockIdx.y * p.segment_keys;
@@ -135,7 +201,7 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
     asm volatile("cp.async.commit_group;\n" ::: "memory");
 
     constexpr int KVEC = RS / 8;
-    auto issue_tile = [&](int j0) {
+    auto issue_tile = [&](int j0, int buf) {
         if (tid < DM_KEYS) {
             const int j = j0 + tid;
             long long off = -1;
@@ -143,14 +209,15 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
                 const int page = table[j / p.page_size];
                 if (page >= 0) off = (long long)(((size_t)page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * RS;
             }
-            key_off[tid] = off;
+            key_off[buf][tid] = off;
         }
         __syncthreads();
+        bf16* dst = ring + (size_t)buf * STAGE_ELEMS;
         for (int e = tid; e < DM_KEYS * KVEC; e += DM_THREADS) {
             const int key = e / KVEC, c = (e % KVEC) * 8;
-            const long long off = key_off[key];
+            const long long off = key_off[buf][key];
             const bool ok = off >= 0;
-            dm_cp_async_16(KVs + key * KSTRIDE + c, ok ? p.pages + off + c : p.pages, ok);
+            dm_cp_async_16(dst + key * KSTRIDE + c, ok ? p.pages + off + c : p.pages, ok);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
@@ -159,7 +226,7 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
     int row_pos[2];
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
-        const int row = warp * 16 + g + 8 * h2;
+        const int row = rw * 16 + g + 8 * h2;
         const int tl = row / hpc, h = row % hpc;
         row_pos[h2] = (tl < ntok && h < heads) ? pos0 + tok0 + tl : -1;
     }
@@ -173,25 +240,40 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
     float l_run[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
 
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    const int warp_first_tok = (warp * 16) / hpc;
-    const int warp_last_tok = (warp * 16 + 15) / hpc;
+    const int warp_first_tok = (rw * 16) / hpc;
+    const int warp_last_tok = (rw * 16 + 15) / hpc;
     const bool warp_has_rows = warp_first_tok < ntok;            // a warp without rows only helps with the copies
     const int warp_hi_pos = pos0 + tok0 + (warp_last_tok < ntok ? warp_last_tok : ntok - 1);
     const int warp_lo_pos = pos0 + tok0 + (warp_first_tok < ntok ? warp_first_tok : ntok - 1);
-    const bf16* Qw = Qs + (size_t)(warp * 16 + (lane & 15)) * QSTRIDE + (lane >> 4) * 8;   // this lane's ldmatrix row of Q
+    const bf16* Qw = Qs + (size_t)(rw * 16 + (lane & 15)) * QSTRIDE + (lane >> 4) * 8;     // this lane's ldmatrix row of Q
+    const bool two = p.stages == 2;
+    if (two && tile_lo <= hi) issue_tile(tile_lo, 0);
+    int buf = 0;
     for (int j0 = tile_lo; j0 <= hi; j0 += DM_KEYS) {
-        issue_tile(j0);
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        if (two) {
+            if (j0 + DM_KEYS <= hi) {
+                issue_tile(j0 + DM_KEYS, buf ^ 1);               // its buffer was read last in the round before: see the barrier below
+                asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+            }
+        } else {
+            issue_tile(j0, 0);
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
         __syncthreads();
+        const bf16* KVs = ring + (size_t)buf * STAGE_ELEMS;
         if (warp_has_rows) {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const int jh = j0 + half * 32;
+                if (split && half != (warp >> 1)) continue;      // another warp's keys
                 if (jh > warp_hi_pos || jh > hi) continue;       // every row of this warp lies before these keys
                 if (p.window > 0 && jh + 31 < warp_lo_pos - p.window + 1) continue;    // or sees none of them any more
                 const bool need_mask = (jh + 31 > warp_lo_pos) || (jh + 31 > hi) || (p.window > 0 && jh < warp_hi_pos - p.window + 1);
 #pragma unroll
                 for (int m = 0; m < 2; ++m) {
+                    if (split && m != (warp & 1)) continue;      // another warp's map
                     float s[4][4];
 #pragma unroll
                     for (int nb = 0; nb < 4; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
@@ -277,6 +359,7 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
             }
         }
         __syncthreads();                                         // the tile's buffer may be overwritten now
+        if (two) buf ^= 1;
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");       // the query copy, where no key tile followed it
 
@@ -289,14 +372,16 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
         }
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
-        const int row = warp * 16 + g + 8 * h2;
+        const int row = rw * 16 + g + 8 * h2;
         const int tl = row / hpc, h = row % hpc;
         const bool exists = row_pos[h2] >= 0;
         if (SEG) {
             if (!exists) continue;
-            float* dst = p.scratch + (((size_t)blockIdx.y * p.total_tokens + (q_begin + tok0 + tl)) * p.nq + (kvh * G + head0 + h)) * (2 * (DV + 2));
+            const size_t set = split ? (size_t)blockIdx.y * 2 + (warp >> 1) : (size_t)blockIdx.y;
+            float* dst = p.scratch + ((set * p.total_tokens + (q_begin + tok0 + tl)) * p.nq + (kvh * G + head0 + h)) * (2 * (DV + 2));
 #pragma unroll
             for (int m = 0; m < 2; ++m) {
+                if (split && m != (warp & 1)) continue;
                 float* d2 = dst + m * (DV + 2);
                 if (t == 0) {
                     d2[0] = m_run[m][h2];
@@ -331,56 +416,25 @@ __global__ void __launch_bounds__(DM_THREADS, 2) diff_attention_mma_kernel(const
         for (int nb = 0; nb < 2 * V16; ++nb)
             *reinterpret_cast<unsigned*>(dst + nb * 8) = dm_pack(o[0][nb][2 * h2] * rn, o[0][nb][2 * h2 + 1] * rn);
     }
-}
-
-// One warp per (token, head): adds the segments' sums of both maps in the order of the segments and combines them.
-// A row's segments are those that hold a key it sees: from the one with its window's first key to the one with its own.
-__global__ void diff_attention_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, long out_stride,
-                                            const int* __restrict__ positions, int total_tokens, int nq, int dv, int window,
-                                            int segment_keys, float lambda, float eps, float out_scale) {
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (row >= total_tokens * nq) return;
-    const int n = row / nq, h = row % nq;
-    const int pos = positions[n];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int s_lo = lo / segment_keys, s_hi = pos / segment_keys;
-    const int w = 2 * (dv + 2);
-    float acc[2][4], m_all[2] = {-INFINITY, -INFINITY}, l_all[2] = {0.f, 0.f};
-#pragma unroll
-    for (int m = 0; m < 2; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) {
-        const float* src = scratch + (((size_t)s * total_tokens + n) * nq + h) * w;
-#pragma unroll
-        for (int m = 0; m < 2; ++m) {
-            const float* s2 = src + m * (dv + 2);
-            const float ms = s2[0], ls = s2[1];
-            const float m_new = fmaxf(m_all[m], ms);
-            const float a_old = exp2f(m_all[m] - m_new), a_new = exp2f(ms - m_new);     // log2 units, as the blocks keep them
-            l_all[m] = l_all[m] * a_old + ls * a_new;
-            m_all[m] = m_new;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int c = lane + 32 * i;
-                if (c < dv) acc[m][i] = acc[m][i] * a_old + s2[2 + c] * a_new;
+    if (SEG) {
+        // every block of this tile whose segment holds one of the tile's keys counts itself once its sums are out; the one
+        // that counts last adds them up
+        __shared__ int is_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int needed = hi_tile / p.segment_keys - lo / p.segment_keys + 1;
+            is_last = atomicAdd(&p.counters[blockIdx.x], 1) == needed - 1;
+            if (is_last) p.counters[blockIdx.x] = 0;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int row = warp; row < ntok * heads; row += DM_THREADS / 32) {
+                const int tl = row / heads, h = row % heads;
+                dm_merge_row(p, q_begin + tok0 + tl, kvh * G + head0 + h, pos0 + tok0 + tl, DV, lane);
             }
         }
-    }
-    const float i1 = 1.f / l_all[0], i2 = lambda / l_all[1];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int c = lane + 32 * i;
-        acc[0][i] = c < dv ? acc[0][i] * i1 - acc[1][i] * i2 : 0.f;
-        ss = fmaf(acc[0][i], acc[0][i], ss);
-    }
-    ss = warp_sum(ss);
-    const float rn = rsqrtf(ss / (float)dv + eps) * out_scale;
-    bf16* dst = out + (size_t)n * out_stride + (size_t)h * dv;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int c = lane + 32 * i;
-        if (c < dv) dst[c] = __float2bfloat16_rn(acc[0][i] * rn);
     }
 }
 
@@ -399,14 +453,15 @@ LLMP_API int llmp_diff_mma_tokens_per_tile(int nq, int nkv) {
     return DM_ROWS / hpc;
 }
 
-// floats of scratch per (segment, token, head)
-LLMP_API int llmp_diff_mma_scratch_floats(int dv) { return 2 * (dv + 2); }
-
 template <int D16, int V16>
 static int launch_diff_mma(const DiffMmaParams& p, unsigned grid, cudaStream_t stream) {
-    const size_t smem = sizeof(bf16) * ((size_t)DM_ROWS * (2 * D16 * 16 + 8) + (size_t)DM_KEYS * (2 * D16 * 16 + V16 * 16 + 8));
+    const size_t q_bytes = sizeof(bf16) * (size_t)DM_ROWS * (2 * D16 * 16 + 8);
+    const size_t stage = sizeof(bf16) * (size_t)DM_KEYS * (2 * D16 * 16 + V16 * 16 + 8);
+    DiffMmaParams q = p;
+    q.stages = q_bytes + 2 * stage <= 110 * 1024 ? 2 : 1;        // two buffers where two blocks of that size still share an SM
+    const size_t smem = q_bytes + q.stages * stage;
     LLMP_ALLOW_SMEM((diff_attention_mma_kernel<D16, V16>), smem);
-    diff_attention_mma_kernel<D16, V16><<<dim3(grid, p.segments > 0 ? p.segments : 1), DM_THREADS, smem, stream>>>(p);
+    diff_attention_mma_kernel<D16, V16><<<dim3(grid, p.segments > 0 ? p.segments : 1), DM_THREADS, smem, stream>>>(q);
     return 0;
 }
 
@@ -414,15 +469,17 @@ LLMP_API int llmp_diff_attention_mma(const void* q, long q_stride, void* out, lo
                                      const int* block_tables, int table_stride, const int* q_start, const int* ctx_len,
                                      const int* positions, const int* tile_req, const int* tile_tok0, int num_tiles, int total_tokens,
                                      int nq, int nkv, int d, int dv, int page_size, int window, float scale, float lambda, float eps,
-                                     float out_scale, int segment_keys, int segments, float* scratch, cudaStream_t stream) {
+                                     float out_scale, int segment_keys, int segments, int split, float* scratch, int* counters,
+                                     cudaStream_t stream) {
     if (num_tiles <= 0 || total_tokens <= 0) return 0;
     LLMP_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && llmp_diff_mma_supports(d, dv, page_size) && page_size > 0 && window >= 0,
                  "diff_attention_mma: sizes heads=%d kv_heads=%d dim=%d vdim=%d are not served", nq, nkv, d, dv);
-    LLMP_REQUIRE(segments == 0 || (scratch && segment_keys > 0 && segment_keys % DM_KEYS == 0 && segments <= 65535),
-                 "diff_attention_mma: segments need scratch and a length that is a multiple of %d", DM_KEYS);
+    LLMP_REQUIRE(segments == 0 || (scratch && counters && segment_keys > 0 && segment_keys % DM_KEYS == 0 && segments <= 65535),
+                 "diff_attention_mma: segments need scratch, counters and a length that is a multiple of %d", DM_KEYS);
     DiffMmaParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.pages = (const bf16*)pages; p.block_tables = block_tables;
     p.q_start = q_start; p.ctx_len = ctx_len; p.tile_req = tile_req; p.tile_tok0 = tile_tok0; p.scratch = scratch;
+    p.counters = counters; p.positions = positions;
     p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv;
     p.page_size = page_size; p.window = window; p.scale = scale; p.lambda = lambda; p.eps = eps; p.out_scale = out_scale;
     const int G = nq / nkv;
@@ -431,6 +488,8 @@ LLMP_API int llmp_diff_attention_mma(const void* q, long q_stride, void* out, lo
     p.head_chunks = (G + p.heads_per_cta - 1) / p.heads_per_cta;
     p.num_tiles = num_tiles;
     p.segment_keys = segment_keys; p.segments = segments; p.total_tokens = total_tokens;
+    p.split = (split && segments > 0) ? 1 : 0; p.stages = 1;
+    LLMP_REQUIRE(!p.split || num_tiles == total_tokens, "diff_attention_mma: warps share a tile's keys only in steps of one token a request");
     LLMP_REQUIRE((long)num_tiles * nkv * p.head_chunks < (1L << 31), "diff_attention_mma: too many tiles");
     LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 2) == 0 && ((size_t)q % 16) == 0 && ((size_t)pages % 16) == 0,
                  "diff_attention_mma: query rows must be 16-byte aligned");
@@ -445,10 +504,5 @@ LLMP_API int llmp_diff_attention_mma(const void* q, long q_stride, void* out, lo
 #undef DM_D
 #undef DM_V
     if (rc) return rc;
-    if (segments > 0) {
-        const int rows = total_tokens * nq;
-        diff_attention_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(scratch, (bf16*)out, out_stride, positions, total_tokens, nq, dv,
-                                                                        window, segment_keys, lambda, eps, out_scale);
-    }
     return llmp_check_launch("diff_attention_mma");
 }

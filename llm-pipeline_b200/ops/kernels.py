@@ -76,7 +76,7 @@ _SIGNATURES = {
     "llmp_diff_qkv_post": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _I, _F, _P, _P, _I, _P, _P, _I, _I, _P],
     "llmp_diff_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P],
     "llmp_diff_attention_mma": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F,
-                                _I, _I, _P, _P],
+                                _I, _I, _I, _P, _P, _P],
 }
 _bound = {}
 launch_count = 0   # kernels of this library launched so far (captured launches count once per capture)
@@ -1132,11 +1132,12 @@ def diff_mma_tokens_per_tile(num_heads: int, num_kv_heads: int) -> int:
 def diff_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
                        positions: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor, out: torch.Tensor, num_heads: int,
                        num_kv_heads: int, dim: int, vdim: int, window: int, scale: float, lam: float, eps: float, out_scale: float,
-                       segments: int = 0) -> torch.Tensor:
+                       segments: int = 0, split: bool = False) -> torch.Tensor:
     """``diff_attention`` on the tensor cores for bfloat16. ``tile_req``/``tile_tok0``: the work list (request and first
     token of every tile of ``diff_mma_tokens_per_tile`` tokens). ``segments`` > 0: the keys are cut into that many segments
-    of ``DIFF_SEGMENT_KEYS`` with blocks of their own, and a second kernel adds them up (steps of few rows over many keys;
-    ``segments`` must cover the longest context)."""
+    of ``DIFF_SEGMENT_KEYS`` with blocks of their own, and the block of a tile that ends last adds them up (steps of few rows over many keys;
+    ``segments`` must cover the longest context). ``split`` (with segments, every tile one token): the four warps of a
+    block share a key tile (half of its keys and one map each) instead of three of them idling."""
     N = q.shape[0]
     _need(q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "diff_attention_mma takes bfloat16")
     _need(q.stride(1) == 1 and q.shape[1] >= 2 * dim * num_heads and out.shape == (N, num_heads * vdim) and out.stride(1) == 1,
@@ -1147,10 +1148,15 @@ def diff_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tenso
                     (tile_tok0, "tile_tok0")):
         _i32(t, name)
     scratch = None
+    # at most one counter per (tile, kv head, chunk of heads); asked for in every call, so that they exist before a step is
+    # captured whose eager run needed no segments
+    counters = attention_counters(q.device, tile_req.numel() * num_heads)
     if segments > 0:
-        scratch = torch.empty(segments * N * num_heads * 2 * (vdim + 2), dtype=torch.float32, device=q.device)
+        _need(not split or tile_req.numel() == N, "warps share a tile's keys only in steps of one token a request")
+        scratch = torch.empty(segments * (2 if split else 1) * N * num_heads * 2 * (vdim + 2), dtype=torch.float32, device=q.device)
     _call("llmp_diff_attention_mma", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(pages), _ptr(tables), tables.shape[1],
           _ptr(q_start), _ptr(ctx_len), _ptr(positions), _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), N, num_heads, num_kv_heads,
           dim, vdim, pages.shape[2], int(window), float(scale), float(lam), float(eps), float(out_scale),
-          DIFF_SEGMENT_KEYS if segments > 0 else 0, int(segments), _ptr(scratch), _stream())
+          DIFF_SEGMENT_KEYS if segments > 0 else 0, int(segments), 1 if split and segments > 0 else 0, _ptr(scratch), _ptr(counters),
+          _stream())
     return out

@@ -130,7 +130,7 @@ class DifferentialAttention(Mixer):
         if blocks < self.SEGMENTS_BELOW_BLOCKS_PER_SM * kernels.sm_count() and reach >= self.SEGMENTS_MIN_CONTEXT:
             segments = -(-longest // kernels.DIFF_SEGMENT_KEYS)
         kernels.diff_attention_mma(qkv, cache.pages, tables, ctx.q_start, ctx.ctx_len, ctx.positions, tile_req, tile_tok0, out, *args,
-                                   segments=segments)
+                                   segments=segments, split=ctx.max_q_len == 1)
 
     def forward(self, x, ctx, cache: LayerCache):
         if cache.pages is None or cache.group is None:

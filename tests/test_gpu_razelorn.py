@@ -153,6 +153,17 @@ def _attention_case(dtype, H_, G, d, dv, window, n, page, seed, plant=None, rot=
             out2 = torch.empty_like(out)
             kernels.diff_attention_mma(qd, pd, table, q_start, ctx_len, positions, torch.zeros_like(tiles), tiles, out2, *args, segments=segments)
             results[f"tensor cores, {segments} segments"] = out2.float().cpu()
+        # a step of single tokens: the last 40 tokens as 40 requests that share the pages, each with one new token; the
+        # four warps of a block then share a key tile
+        last = 40
+        rows = torch.arange(n - last, n, device=dev)
+        out3 = torch.empty(last, H_ * dv, device=dev, dtype=dtype)
+        ones = torch.arange(last + 1, dtype=torch.int32, device=dev)
+        kernels.diff_attention_mma(qd[rows].contiguous(), pd, table.expand(last, -1).contiguous(), ones, (rows + 1).to(torch.int32),
+                                   positions[rows].contiguous(), torch.arange(last, dtype=torch.int32, device=dev),
+                                   torch.zeros(last, dtype=torch.int32, device=dev), out3, *args,
+                                   segments=-(-n // kernels.DIFF_SEGMENT_KEYS), split=True)
+        results["tensor cores, single tokens"] = torch.cat([want[:n - last].float(), out3.float().cpu()])
     return results, want
 
 
@@ -164,7 +175,7 @@ def test_attention_kernels_alone(dtype, sizes):
     shuffled pages: the general kernel in both types, the tensor-core kernel whole and in key segments in bfloat16."""
     H_, G, d, dv, window = sizes
     results, want = _attention_case(dtype, H_, G, d, dv, window, n=330, page=16, seed=3)
-    assert dtype != torch.bfloat16 or d % 16 or len(results) == 3
+    assert dtype != torch.bfloat16 or d % 16 or len(results) == 4
     for name, got in results.items():
         assert (got.double() - want).abs().max() < (2e-4 if dtype == torch.float32 else 4e-2), name
 

@@ -47,7 +47,6 @@ def test_layers_that_use_another_layers_tensors_run_its_parts_with_a_cache_of_th
     (lambda c: c["layers"][1]["mlp"].update(kind="glu"), "unknown mlp kind"),
     (lambda c: c["layers"][2].update(weights_of=2), "weights_of"),
     (lambda c: c["layers"][2].update(weights_of=4), "weights_of"),
-    (lambda c: c["layers"][2]["mixer"].update(heads=12), "describes another layer"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=34), "rot.dims"),
     (lambda c: c["layers"][0]["mixer"].update(heads=7), "cannot share"),
     (lambda c: c.pop("norm"), "required keys"),
@@ -59,6 +58,14 @@ def test_refusals(damage, message):
     damage(cfg)
     with pytest.raises(ValueError, match=message):
         resolve_config(cfg)
+
+
+def test_a_layer_that_uses_another_layers_tensors_is_described_by_that_layer():
+    from llm_pipeline_b200.config import resolve_config
+
+    cfg = copy.deepcopy(R.CONFIGS["mixed"])
+    cfg["layers"][2] = {"type": "attention", "weights_of": 0}
+    assert resolve_config(cfg).model_spec() == resolve_config(R.CONFIGS["mixed"]).model_spec()
 
 
 def test_rescaled_frequencies_follow_the_plain_rule():
