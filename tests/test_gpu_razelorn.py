@@ -169,10 +169,11 @@ def _attention_case(dtype, H_, G, d, dv, window, n, page, seed, plant=None, rot=
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("sizes", [(4, 2, 16, 32, 24), (3, 3, 12, 20, 9), (6, 1, 48, 48, None), (2, 2, 128, 64, 300), (32, 2, 16, 16, 70),
-                                   (1, 1, 64, 128, 64)], ids=str)
+                                   (1, 1, 64, 128, 64), (40, 1, 16, 32, None)], ids=str)
 def test_attention_kernels_alone(dtype, sizes):
-    """Both maps, grouped heads, values of another width than keys, windows below, at and above a tile of keys, over
-    shuffled pages: the general kernel in both types, the tensor-core kernel whole and in key segments in bfloat16."""
+    """Both maps, grouped heads (also more of them on a key/value head than a tile's 16 rows a token), values of another
+    width than keys, windows below, at and above a tile of keys, over shuffled pages: the general kernel in both types, the
+    tensor-core kernel whole, in key segments and for single tokens in bfloat16."""
     H_, G, d, dv, window = sizes
     results, want = _attention_case(dtype, H_, G, d, dv, window, n=330, page=16, seed=3)
     assert dtype != torch.bfloat16 or d % 16 or len(results) == 4
@@ -363,6 +364,25 @@ def test_long_decoding_through_replayed_graphs(tmp_path, dtype):
     assert runner.graph_replays > 200
     for rid in requests:
         R.assert_matches({rid: torch.cat(rows[rid])}, {rid: want[rid][:231]}, dtype, f"long decoding of {rid}", share_for(cfg, dtype))
+
+
+def test_decoding_through_graphs_across_the_length_where_key_segments_begin(tmp_path):
+    """bfloat16 without a window: a request decodes from below two segments of keys to above them. The first step of a
+    shape runs eagerly with its real length (no segments yet), the captured step is sized for the longest context its
+    block tables can hold (segments): what the segments need must exist before the capture."""
+    from llm_pipeline_b200.engine import StepEntry
+    from llm_pipeline_b200.ops import kernels
+    cfg, W, folder = case(tmp_path, "no_window", 9, sharp=4.0)
+    first = 2 * kernels.DIFF_SEGMENT_KEYS - 40
+    requests = requests_for(cfg, [first + 80], 800)
+    want = R.oracle(cfg, W, requests)
+    runner = H.make_runner(folder, torch.bfloat16, page_size=16, num_pages=48, max_request_tokens=768, max_requests=2)
+    toks = requests["r0"]
+    rows = [runner.step([StepEntry("r0", toks[:first], list(range(first)))]).float().cpu()]
+    for t in range(first, len(toks)):
+        rows.append(runner.step([StepEntry("r0", [toks[t]], [0])]).float().cpu())
+    assert runner.graph_replays > 60
+    R.assert_matches({"r0": torch.cat(rows)}, want, torch.bfloat16, "decoding across the first segment border", 0.85)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
